@@ -13,18 +13,20 @@ from ..errors import CapacityError, InvalidArgument
 
 
 class StateSlots:
-    def __init__(self, needs, max_requests: int, device=None):
-        """needs[i]: parts.StateNeed or None per run entry."""
+    def __init__(self, needs, max_requests: int, device=None, extra=None):
+        """needs[i]: parts.StateNeed or None per run entry; extra: {name: StateNeed} for state that belongs to no run
+        entry (an embedding that remembers a request's last token)."""
         if max_requests <= 0:
             raise InvalidArgument(f"state slots need a positive request count, got {max_requests}")
         self.max_requests = max_requests
         self._free = list(range(max_requests - 1, -1, -1))
         self._used = [False] * max_requests
         self._tensors = {}
-        self.has_state = any(need is not None for need in needs)
+        extra = dict(extra or {})
+        self.has_state = any(need is not None for need in needs) or bool(extra)
         if device is not None:
             import torch
-            for i, need in enumerate(needs):
+            for i, need in list(enumerate(needs)) + list(extra.items()):
                 if need is not None:
                     self._tensors[i] = torch.zeros((max_requests, *need.shape), dtype=need.dtype, device=device)
         self.bytes_per_slot = sum(t[0].numel() * t.element_size() for t in self._tensors.values())
@@ -53,3 +55,7 @@ class StateSlots:
 
     def tensor(self, entry: int):
         return self._tensors.get(entry)
+
+    def extra(self, name: str):
+        """The [slots, ...] tensor of a state that was asked for by name."""
+        return self._tensors.get(name)

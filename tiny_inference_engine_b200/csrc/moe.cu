@@ -1,8 +1,10 @@
 // A feed-forward made of many small experts of which each token uses a few.
 //
-//   moe_route   one warp per token: softmax over all experts' logits (float), the best `keep` of `groups` equal
-//               blocks of consecutive experts by their best member, then the `top` best experts of those groups
-//               (ties go to the lower index); weights are the chosen scores over their sum (+ 1e-20).
+//   moe_route   one warp per token: scores from all experts' logits (float; a softmax over the experts, or a sigmoid
+//               each), choice scores = scores + an optional correction per expert, the best `keep` of `groups` equal
+//               blocks of consecutive experts by their best member (or by the sum of their few best), then the `top`
+//               best experts of those groups by choice score (ties go to the lower index); weights are the chosen
+//               experts' scores, over their sum (+ 1e-20) or as they are.
 //   moe_align   one block: counts the (token, choice) pairs of every expert, gives each expert a range of rows
 //               that is a whole number of tiles of `block_m` rows, and lists the pairs in that order (-1 pads a
 //               tile). Also says which expert each tile belongs to and how many tiles there are, all on the
@@ -35,9 +37,14 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 }
 
 // smem per warp: experts floats (scores), experts floats (work), groups floats, groups ints.
+// score_fn 0: s = softmax over all experts; 1: s = sigmoid of each logit. Experts are chosen by s + correction
+// (correction null: by s); a group counts as the sum of its `group_top` largest choice scores (1: its best member);
+// experts outside the kept groups cannot be chosen (their choice score counts as minus infinity: choice scores may be
+// negative). The weights are the chosen experts' s, over their sum (+ 1e-20) when `renorm`, else as they are.
 __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, long long ld_logits, int tokens,
-                                                        int experts, int top, int groups, int keep, int* __restrict__ ids,
-                                                        float* __restrict__ weights) {
+                                                        int experts, int top, int groups, int keep, int score_fn,
+                                                        const float* __restrict__ correction, int group_top, int renorm,
+                                                        int* __restrict__ ids, float* __restrict__ weights) {
   pdl_sync();
   extern __shared__ float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -48,29 +55,41 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
   float* gbest = work + experts;
   int* gsel = reinterpret_cast<int*>(gbest + groups);
   const float* z = logits + t * ld_logits;
-  float m = -INFINITY;
-  for (int e = lane; e < experts; e += 32) m = fmaxf(m, z[e]);
-  m = warp_max(m);
-  float sum = 0.0f;
-  for (int e = lane; e < experts; e += 32) {
-    const float p = expf(z[e] - m);
-    score[e] = p;
-    sum += p;
+  if (score_fn == 0) {
+    float m = -INFINITY;
+    for (int e = lane; e < experts; e += 32) m = fmaxf(m, z[e]);
+    m = warp_max(m);
+    float sum = 0.0f;
+    for (int e = lane; e < experts; e += 32) {
+      const float p = expf(z[e] - m);
+      score[e] = p;
+      sum += p;
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+    for (int e = lane; e < experts; e += 32) score[e] *= inv;
+  } else {
+    for (int e = lane; e < experts; e += 32) score[e] = 1.0f / (1.0f + expf(-z[e]));
   }
-  sum = warp_sum(sum);
-  const float inv = 1.0f / sum;
-  for (int e = lane; e < experts; e += 32) {
-    const float s = score[e] * inv;
-    score[e] = s;
-    work[e] = s;
-  }
+  for (int e = lane; e < experts; e += 32) work[e] = score[e] + (correction != nullptr ? correction[e] : 0.0f);
   __syncwarp();
   const int per = experts / groups;
   if (keep < groups) {
     for (int g = lane; g < groups; g += 32) {
-      float b = -1.0f;
-      for (int e = g * per; e < (g + 1) * per; ++e) b = fmaxf(b, score[e]);
-      gbest[g] = b;
+      // the sum of the group's `group_top` largest choice scores: pick the largest that is left, that often
+      float total = 0.0f;
+      unsigned long long taken = 0ull;        // members picked so far (the launcher allows group_top > 1 for up to 64 members)
+      for (int k = 0; k < min(group_top, per); ++k) {
+        float b = -INFINITY;
+        int bi = -1;
+        for (int e = 0; e < per; ++e) {
+          const bool used = k > 0 && ((taken >> e) & 1ull) != 0ull;
+          if (!used && (bi < 0 || work[g * per + e] > b)) b = work[g * per + e], bi = e;
+        }
+        total += b;
+        taken |= 1ull << (bi & 63);
+      }
+      gbest[g] = total;
       gsel[g] = 0;
     }
     __syncwarp();
@@ -78,14 +97,15 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
       float bv = -INFINITY;
       int bi = 0x7fffffff;
       for (int g = lane; g < groups; g += 32)
-        if (gbest[g] > bv) bv = gbest[g], bi = g;
+        if (!gsel[g] && (bi == 0x7fffffff || gbest[g] > bv)) bv = gbest[g], bi = g;
       warp_argmax(bv, bi);
       if (bi >= groups) bi = k;            // nothing comparable (a row of NaN): any group
-      if (lane == 0) gsel[bi] = 1, gbest[bi] = -2.0f;
+      __syncwarp();
+      if (lane == 0) gsel[bi] = 1;
       __syncwarp();
     }
     for (int e = lane; e < experts; e += 32)
-      if (!gsel[e / per]) work[e] = -1.0f;
+      if (!gsel[e / per]) work[e] = -INFINITY;
     __syncwarp();
   }
   float total = 0.0f;
@@ -102,12 +122,12 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
     total += s;
     if (lane == (k & 31)) mine_w = s, mine_e = bi;     // top <= 32 is checked by the launcher
     __syncwarp();
-    if (lane == 0) work[bi] = -1.0f;
+    if (lane == 0) work[bi] = -INFINITY;
     __syncwarp();
   }
   if (lane < top) {
     ids[t * top + lane] = mine_e;
-    weights[t * top + lane] = mine_w / (total + 1e-20f);
+    weights[t * top + lane] = renorm ? mine_w / (total + 1e-20f) : mine_w;
   }
 }
 
@@ -383,14 +403,19 @@ TIE_API int tie_moe_combine(int dtype, const void* y, const int* sorted, const i
 }
 
 TIE_API int tie_moe_route(const float* logits, long long ld_logits, int tokens, int experts, int top, int groups, int keep,
-                          int* ids, float* weights, cudaStream_t s) {
+                          int score_fn, const float* correction, int group_top, int renorm, int* ids, float* weights,
+                          cudaStream_t s) {
+  TIE_REQUIRE((score_fn == 0 || score_fn == 1) && group_top >= 1, "moe_route: score function %d, %d members a group's score",
+              score_fn, group_top);
+  TIE_REQUIRE(group_top == 1 || experts / (groups > 0 ? groups : 1) <= 64, "moe_route: groups of more than 64 experts count their best member only");
   TIE_REQUIRE(experts > 0 && top > 0 && top <= 32 && top <= experts && groups > 0 && experts % groups == 0 && keep > 0 &&
                   keep <= groups && top <= keep * (experts / groups),
               "moe_route: bad routing experts=%d top=%d (at most 32) groups=%d keep=%d", experts, top, groups, keep);
   if (tokens <= 0) return kOk;
   const size_t smem = 4 * sizeof(float) * (2 * experts + 2 * groups);
   TIE_REQUIRE(smem <= 48 * 1024, "moe_route: %d experts exceed the kernel's shared memory", experts);
-  TIE_LAUNCH(moe_route_kernel, ceil_div(tokens, 4), 128, smem, s, logits, ld_logits, tokens, experts, top, groups, keep, ids, weights);
+  TIE_LAUNCH(moe_route_kernel, ceil_div(tokens, 4), 128, smem, s, logits, ld_logits, tokens, experts, top, groups, keep, score_fn,
+             correction, group_top, renorm, ids, weights);
   TIE_RETURN_LAUNCH("moe_route");
 }
 

@@ -1,0 +1,359 @@
+// Kernels of a layer whose two sublayers read the same stream side by side, and of what such models put around it:
+//
+//   pair_hash_add     x[t] += table[row], row = (prev * mul_prev + token * mul_cur) mod buckets for the pair (previous
+//                     token, token), or the table's last row for a sequence's first token. The previous token of a
+//                     portion's first row comes from the request's state slot; the block of that row also stores the
+//                     portion's last token there (no other block touches the slot).
+//   add_row_vector    x[t] += vec for every row (one learned vector ahead of a pass over a span of layers).
+//   group_norm_taps   u = x / rms over each of `groups` equal parts of the row (float). Outputs, one per sublayer:
+//                     out_a = w_a * (u_t + sum_j taps_a[:, j] * u_(t - taps + 1 + j)), that is h + conv(h) for h = u * w_a,
+//                     a causal convolution over time per channel with zeros ahead of the sequence. Rows of this step
+//                     are renormed from x (x is complete when the kernel starts); rows of earlier steps come from the
+//                     request's state, a ring of the last taps - 1 unit rows indexed by position. The rows that will
+//                     be that ring after the step are left in `unit`; parallel_finish moves them (it runs when every
+//                     block here has read the ring). With taps = 0 it is a plain grouped norm, optionally over
+//                     gathered rows and with a delta added to x first.
+//   parallel_finish   x += mult * (delta_a + delta_b) (tensors or float partial sums, added in order), then the token
+//                     side input: g = gelu_tanh(W_gate x) * table[token], y = W_proj g, x += mult * y / rms(y) * w;
+//                     then the ring update. Sums, norms and the stream in float.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace tie {
+
+template <typename T>
+__global__ void __launch_bounds__(128) pair_hash_add_kernel(float* __restrict__ x, const T* __restrict__ table,
+                                                            const int* __restrict__ tokens, const int* __restrict__ positions,
+                                                            const int* __restrict__ seq_of_row, const int* __restrict__ query_start,
+                                                            const int* __restrict__ state_slots, int* __restrict__ prev_state,
+                                                            int buckets, long long mul_prev, long long mul_cur, int dim) {
+  pdl_sync();
+  __shared__ int srow;
+  const int t = blockIdx.x;
+  if (threadIdx.x == 0) {
+    const int s = seq_of_row[t], pos = positions[t], q0 = query_start[s];
+    const int slot = state_slots[s];
+    int row = buckets;
+    if (pos > 0) {
+      const long long prev = t > q0 ? tokens[t - 1] : (slot >= 0 ? prev_state[slot] : 0);
+      long long r = (prev * mul_prev + static_cast<long long>(tokens[t]) * mul_cur) % buckets;
+      if (r < 0) r += buckets;
+      row = static_cast<int>(r);
+    }
+    srow = row;
+    if (t == q0 && slot >= 0) prev_state[slot] = tokens[query_start[s + 1] - 1];
+  }
+  __syncthreads();
+  const T* src = table + static_cast<long long>(srow) * dim;
+  float* xr = x + static_cast<long long>(t) * dim;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) xr[d] += ld(src + d);
+}
+
+__global__ void __launch_bounds__(256) add_row_vector_kernel(float* __restrict__ x, const float* __restrict__ vec, int dim,
+                                                             long long total) {
+  pdl_sync();
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < total) x[i] += vec[i % dim];
+}
+
+constexpr int kMaxTaps = 8;
+
+struct Delta {            // what a sublayer hands on: a tensor in the storage type, or float partial sums, or nothing
+  const void* tensor;
+  const float* part;
+  long long part_stride;
+  int splits;
+};
+
+template <typename T>
+__device__ __forceinline__ float delta_at(const Delta& d, long long idx) {
+  if (d.tensor != nullptr) return ld(static_cast<const T*>(d.tensor) + idx);
+  float y = 0.0f;
+  if (d.part != nullptr)
+    for (int z = 0; z < d.splits; ++z) y += d.part[z * d.part_stride + idx];
+  return y;
+}
+
+struct NormTapsArgs {
+  float* x;                 // [T, D]
+  Delta delta;              // taps == 0 only: added to x first (written back unless rows are gathered)
+  const int* rows;          // taps == 0 only: output row i reads row rows[i] (null: i)
+  int n, D, groups;
+  float eps;
+  const float* w_a;
+  const float* w_b;         // null: one output
+  const float* taps_a;      // [D, taps] float (null with taps == 0)
+  const float* taps_b;
+  int taps;
+  void* out_a;
+  void* out_b;
+  float* unit;              // [T, D]
+  const float* ring;        // [slots, taps - 1, D]
+  const int* seq_of_row;
+  const int* positions;
+  const int* query_start;
+  const int* context_lens;
+  const int* state_slots;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) group_norm_taps_kernel(NormTapsArgs a) {
+  pdl_sync();
+  extern __shared__ float smem[];
+  float* inv = smem;                       // [(R + 1) * groups]
+  const int i = blockIdx.x;
+  const int t = a.rows != nullptr ? a.rows[i] : i;
+  const int D = a.D, R = a.taps > 0 ? a.taps - 1 : 0;
+  const int gsize = D / a.groups;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  int pos = 0, first = 0, slot = -1, ctx = 0;
+  if (a.taps > 0) {
+    const int s = a.seq_of_row[t];
+    pos = a.positions[t];
+    first = pos - (t - a.query_start[s]);      // position of the portion's first row
+    slot = a.state_slots[s];
+    ctx = a.context_lens[s];
+  }
+  float* xr = a.x + static_cast<long long>(t) * D;
+  if (a.taps == 0 && (a.delta.tensor != nullptr || a.delta.part != nullptr)) {
+    float* row = smem + a.groups;          // the summed row, kept for both passes
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+      const float v = xr[d] + delta_at<T>(a.delta, static_cast<long long>(t) * D + d);
+      row[d] = v;
+      if (a.rows == nullptr) xr[d] = v;
+    }
+    __syncthreads();
+    xr = row;
+  }
+  for (int item = warp; item < (R + 1) * a.groups; item += nwarps) {
+    const int r = item / a.groups, g = item - r * a.groups;
+    if (r > 0 && pos - r < first) continue;      // a row of an earlier step (or none): no norm to compute
+    const float* src = xr - static_cast<long long>(r) * D + g * gsize;
+    float ss = 0.0f;
+    for (int d = lane; d < gsize; d += 32) ss = fmaf(src[d], src[d], ss);
+    ss = warp_sum(ss);
+    if (lane == 0) inv[item] = 1.0f / sqrtf(ss / static_cast<float>(gsize) + a.eps);
+  }
+  __syncthreads();
+  const bool keep = a.taps > 1 && pos >= ctx - R;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    const int g = d / gsize;
+    float u[kMaxTaps];
+    u[0] = xr[d] * inv[g];
+#pragma unroll
+    for (int r = 1; r < kMaxTaps; ++r) {
+      if (r > R) break;
+      const int p = pos - r;
+      float v = 0.0f;
+      if (p >= first) v = xr[d - static_cast<long long>(r) * D] * inv[r * a.groups + g];
+      else if (p >= 0 && slot >= 0) v = a.ring[(static_cast<long long>(slot) * R + p % R) * D + d];
+      u[r] = v;
+    }
+    float sa = u[0], sb = u[0];
+    if (a.taps > 0) {
+#pragma unroll
+      for (int j = 0; j < kMaxTaps; ++j) {
+        if (j >= a.taps) break;
+        const float v = u[a.taps - 1 - j];
+        sa = fmaf(a.taps_a[static_cast<long long>(d) * a.taps + j], v, sa);
+        if (a.w_b != nullptr) sb = fmaf(a.taps_b[static_cast<long long>(d) * a.taps + j], v, sb);
+      }
+    }
+    st(static_cast<T*>(a.out_a) + static_cast<long long>(i) * D + d, a.w_a[d] * sa);
+    if (a.w_b != nullptr) st(static_cast<T*>(a.out_b) + static_cast<long long>(i) * D + d, a.w_b[d] * sb);
+    if (keep) a.unit[static_cast<long long>(t) * D + d] = u[0];
+  }
+}
+
+__device__ __forceinline__ float gelu_tanh_side(float z) {
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+struct FinishArgs {
+  float* x;
+  int T, D;
+  float mult;
+  Delta a, b;
+  // token side input (side_dim == 0: none)
+  const int* tokens;
+  const void* side_table;      // [vocab, side_dim] in the storage type
+  const void* side_gate;       // [side_dim, D]
+  const void* side_proj;       // [D, side_dim]
+  const float* side_norm;      // [D]
+  int side_dim;
+  float eps;
+  // ring of unit rows (R == 0: none)
+  const float* unit;
+  float* ring;
+  int R;
+  const int* seq_of_row;
+  const int* positions;
+  const int* context_lens;
+  const int* state_slots;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) parallel_finish_kernel(FinishArgs a) {
+  pdl_sync();
+  extern __shared__ float smem[];
+  float* row = smem;                   // [D]
+  float* g = row + a.D;                // [side_dim]
+  float* scratch = g + a.side_dim;     // [33]
+  const int t = blockIdx.x, D = a.D;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  float* xr = a.x + static_cast<long long>(t) * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    const long long idx = static_cast<long long>(t) * D + d;
+    const float v = xr[d] + a.mult * (delta_at<T>(a.a, idx) + delta_at<T>(a.b, idx));
+    row[d] = v;
+    if (a.side_dim == 0) xr[d] = v;
+  }
+  if (a.side_dim > 0) {
+    __syncthreads();
+    const int tok = a.tokens[t];
+    for (int i = warp; i < a.side_dim; i += nwarps) {
+      const T* wr = static_cast<const T*>(a.side_gate) + static_cast<long long>(i) * D;
+      float dot = 0.0f;
+      for (int d = lane; d < D; d += 32) dot = fmaf(ld(wr + d), row[d], dot);
+      dot = warp_sum(dot);
+      if (lane == 0) g[i] = gelu_tanh_side(dot) * ld(static_cast<const T*>(a.side_table) + static_cast<long long>(tok) * a.side_dim + i);
+    }
+    __syncthreads();
+    float ss = 0.0f;
+    // y is formed twice (for its norm, then for the sum): side_dim terms an element
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+      const T* wr = static_cast<const T*>(a.side_proj) + static_cast<long long>(d) * a.side_dim;
+      float y = 0.0f;
+      for (int i = 0; i < a.side_dim; ++i) y = fmaf(ld(wr + i), g[i], y);
+      ss = fmaf(y, y, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / static_cast<float>(D) + a.eps);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+      const T* wr = static_cast<const T*>(a.side_proj) + static_cast<long long>(d) * a.side_dim;
+      float y = 0.0f;
+      for (int i = 0; i < a.side_dim; ++i) y = fmaf(ld(wr + i), g[i], y);
+      xr[d] = row[d] + a.mult * (y * inv) * a.side_norm[d];
+    }
+  }
+  if (a.R > 0) {
+    const int s = a.seq_of_row[t];
+    const int pos = a.positions[t], slot = a.state_slots[s];
+    if (slot >= 0 && pos >= a.context_lens[s] - a.R) {
+      const float* src = a.unit + static_cast<long long>(t) * D;
+      float* dst = a.ring + (static_cast<long long>(slot) * a.R + pos % a.R) * D;
+      for (int d = threadIdx.x; d < D; d += blockDim.x) dst[d] = src[d];
+    }
+  }
+}
+
+}  // namespace tie
+
+using namespace tie;
+
+TIE_API int tie_pair_hash_add(int dtype, float* x, const void* table, const int* tokens, const int* positions,
+                              const int* seq_of_row, const int* query_start, const int* state_slots, int* prev_state,
+                              int buckets, long long mul_prev, long long mul_cur, int rows, int dim, cudaStream_t s) {
+  TIE_REQUIRE(rows >= 0 && dim > 0 && buckets > 0 && prev_state != nullptr, "pair_hash_add: bad sizes rows=%d dim=%d buckets=%d",
+              rows, dim, buckets);
+  if (rows == 0) return kOk;
+  if (dtype == TIE_F32) {
+    TIE_LAUNCH((pair_hash_add_kernel<float>), rows, 128, 0, s, x, static_cast<const float*>(table), tokens, positions, seq_of_row,
+               query_start, state_slots, prev_state, buckets, mul_prev, mul_cur, dim);
+  } else if (dtype == TIE_BF16) {
+    TIE_LAUNCH((pair_hash_add_kernel<__nv_bfloat16>), rows, 128, 0, s, x, static_cast<const __nv_bfloat16*>(table), tokens,
+               positions, seq_of_row, query_start, state_slots, prev_state, buckets, mul_prev, mul_cur, dim);
+  } else {
+    set_error("pair_hash_add: unknown dtype code %d", dtype);
+    return kBadArgument;
+  }
+  TIE_RETURN_LAUNCH("pair_hash_add");
+}
+
+TIE_API int tie_add_row_vector(float* x, const float* vec, int rows, int dim, cudaStream_t s) {
+  TIE_REQUIRE(rows >= 0 && dim > 0 && x != nullptr && vec != nullptr, "add_row_vector: bad arguments rows=%d dim=%d", rows, dim);
+  const long long total = static_cast<long long>(rows) * dim;
+  if (total == 0) return kOk;
+  TIE_LAUNCH(add_row_vector_kernel, ceil_div(total, 256), 256, 0, s, x, vec, dim, total);
+  TIE_RETURN_LAUNCH("add_row_vector");
+}
+
+TIE_API int tie_group_norm_taps(int dtype, float* x, const void* delta, const float* part, long long part_stride, int splits,
+                                const int* rows, int n, int dim, int groups, float eps, const float* w_a, const float* w_b,
+                                const float* taps_a, const float* taps_b, int taps, void* out_a, void* out_b, float* unit,
+                                const float* ring, const int* seq_of_row, const int* positions, const int* query_start,
+                                const int* context_lens, const int* state_slots, cudaStream_t s) {
+  TIE_REQUIRE(n >= 0 && dim > 0 && groups > 0 && dim % groups == 0, "group_norm_taps: %d columns do not split into %d equal groups",
+              dim, groups);
+  TIE_REQUIRE(taps >= 0 && taps <= kMaxTaps, "group_norm_taps: at most %d taps, got %d", kMaxTaps, taps);
+  TIE_REQUIRE(w_a != nullptr && out_a != nullptr && (w_b == nullptr || out_b != nullptr), "group_norm_taps: an output without a buffer");
+  TIE_REQUIRE(taps == 0 || (taps_a != nullptr && (w_b == nullptr || taps_b != nullptr) && seq_of_row != nullptr && positions != nullptr &&
+                            query_start != nullptr && context_lens != nullptr && state_slots != nullptr &&
+                            (taps == 1 || (unit != nullptr && ring != nullptr))),
+              "group_norm_taps: taps need their weights, the step's index arrays and the state ring");
+  TIE_REQUIRE(taps == 0 || (rows == nullptr && delta == nullptr && part == nullptr),
+              "group_norm_taps: gathered rows and a delta go with taps = 0 only (the rows before a row are renormed from x)");
+  TIE_REQUIRE(part == nullptr || (delta == nullptr && splits >= 1), "group_norm_taps: give a delta or partial sums, not both");
+  if (n == 0) return kOk;
+  NormTapsArgs a{};
+  a.x = x;
+  a.delta = Delta{delta, part, part_stride, splits};
+  a.rows = rows;
+  a.n = n, a.D = dim, a.groups = groups, a.eps = eps;
+  a.w_a = w_a, a.w_b = w_b, a.taps_a = taps_a, a.taps_b = taps_b, a.taps = taps;
+  a.out_a = out_a, a.out_b = out_b, a.unit = unit, a.ring = ring;
+  a.seq_of_row = seq_of_row, a.positions = positions, a.query_start = query_start, a.context_lens = context_lens;
+  a.state_slots = state_slots;
+  const bool summed = taps == 0 && (delta != nullptr || part != nullptr);
+  const size_t smem = (static_cast<size_t>(taps > 0 ? taps : 1) * groups + (summed ? dim : 0)) * sizeof(float);
+  TIE_REQUIRE(smem <= 200 * 1024, "group_norm_taps: a row of %d columns does not fit shared memory", dim);
+  if (dtype == TIE_F32) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(group_norm_taps_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    TIE_LAUNCH((group_norm_taps_kernel<float>), n, 256, smem, s, a);
+  } else if (dtype == TIE_BF16) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(group_norm_taps_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    TIE_LAUNCH((group_norm_taps_kernel<__nv_bfloat16>), n, 256, smem, s, a);
+  } else {
+    set_error("group_norm_taps: unknown dtype code %d", dtype);
+    return kBadArgument;
+  }
+  TIE_RETURN_LAUNCH("group_norm_taps");
+}
+
+TIE_API int tie_parallel_finish(int dtype, float* x, int rows, int dim, float mult, const void* delta_a, const float* part_a,
+                                long long stride_a, int splits_a, const void* delta_b, const float* part_b, long long stride_b,
+                                int splits_b, const int* tokens, const void* side_table, const void* side_gate,
+                                const void* side_proj, const float* side_norm, int side_dim, float eps, const float* unit,
+                                float* ring, int ring_rows, const int* seq_of_row, const int* positions,
+                                const int* context_lens, const int* state_slots, cudaStream_t s) {
+  TIE_REQUIRE(rows >= 0 && dim > 0 && side_dim >= 0 && ring_rows >= 0, "parallel_finish: bad sizes rows=%d dim=%d", rows, dim);
+  TIE_REQUIRE((delta_a == nullptr || part_a == nullptr) && (delta_b == nullptr || part_b == nullptr),
+              "parallel_finish: give a delta or partial sums, not both");
+  TIE_REQUIRE(side_dim == 0 || (tokens != nullptr && side_table != nullptr && side_gate != nullptr && side_proj != nullptr &&
+                                side_norm != nullptr), "parallel_finish: the token side input needs its tensors");
+  TIE_REQUIRE(ring_rows == 0 || (unit != nullptr && ring != nullptr && seq_of_row != nullptr && positions != nullptr &&
+                                 context_lens != nullptr && state_slots != nullptr), "parallel_finish: the ring needs the step's index arrays");
+  if (rows == 0) return kOk;
+  FinishArgs a{};
+  a.x = x, a.T = rows, a.D = dim, a.mult = mult;
+  a.a = Delta{delta_a, part_a, stride_a, splits_a};
+  a.b = Delta{delta_b, part_b, stride_b, splits_b};
+  a.tokens = tokens, a.side_table = side_table, a.side_gate = side_gate, a.side_proj = side_proj, a.side_norm = side_norm;
+  a.side_dim = side_dim, a.eps = eps;
+  a.unit = unit, a.ring = ring, a.R = ring_rows;
+  a.seq_of_row = seq_of_row, a.positions = positions, a.context_lens = context_lens, a.state_slots = state_slots;
+  const size_t smem = (static_cast<size_t>(dim) + side_dim + 40) * sizeof(float);
+  TIE_REQUIRE(smem <= 200 * 1024, "parallel_finish: a row of %d columns does not fit shared memory", dim);
+  if (dtype == TIE_F32) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(parallel_finish_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    TIE_LAUNCH((parallel_finish_kernel<float>), rows, 256, smem, s, a);
+  } else if (dtype == TIE_BF16) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(parallel_finish_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    TIE_LAUNCH((parallel_finish_kernel<__nv_bfloat16>), rows, 256, smem, s, a);
+  } else {
+    set_error("parallel_finish: unknown dtype code %d", dtype);
+    return kBadArgument;
+  }
+  TIE_RETURN_LAUNCH("parallel_finish");
+}

@@ -47,7 +47,7 @@ def make_cache(model: Model, page_size: int = 16, num_pages: int | None = None, 
     """The cache and the state slots of a model. `max_requests` is how many requests can hold state of fixed
     size at once; with `window_requests` layers that keep a window of keys get pages for that many requests
     only (`CacheManager`), the rest of the budget goes to the layers that keep every key."""
-    states = StateSlots(model.state_needs(), max_requests, device=device)
+    states = StateSlots(model.state_needs(), max_requests, device=device, extra=model.extra_state_needs())
     cache = CacheManager(model.cache_needs(), page_size, num_pages=num_pages, budget_bytes=kv_mem, dtype=model.dtype,
                          device=device, state_slots=states, window_requests=window_requests,
                          window_step_tokens=window_step_tokens)

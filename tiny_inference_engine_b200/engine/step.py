@@ -162,7 +162,9 @@ class StepRunner:
         self.fail_hook = None     # tests: called after the batch is built, may raise
         # A mixer with state of its own may be plain torch code that reads the step on the host: decode steps are
         # captured as graphs only if every such mixer says that it can be (`Mixer.graph_safe`).
-        stateful = [model.layers[e.layer].mixer for i, e in enumerate(model.spec.run_order)
+        def state_part(block):
+            return block.state_part() if hasattr(block, "state_part") else block.mixer
+        stateful = [state_part(model.layers[e.layer]) for i, e in enumerate(model.spec.run_order)
                     if states is not None and states.tensor(i) is not None]
         self.use_graphs = use_graphs and all(getattr(m, "graph_safe", False) for m in stateful)
         self._graphs: dict[tuple, tuple] = {}

@@ -980,16 +980,24 @@ def glu_biased(gate_up, bias_gate, bias_up, out, act: int = ACT_SILU) -> None:
 
 # -- experts (csrc/moe.cu)
 
-def moe_route(logits, top: int, groups: int, keep: int, ids, weights) -> None:
-    """Per token: softmax over all experts, the `keep` best of `groups` equal blocks of consecutive experts (a group counts as much
-    as its best member), the `top` best experts of those; ids int32 [T, top], weights float32 [T, top] = the chosen scores
-    over their sum (+ 1e-20)."""
-    _dev(logits, ids, weights)
+ROUTE_SOFTMAX, ROUTE_SIGMOID = 0, 1
+
+
+def moe_route(logits, top: int, groups: int, keep: int, ids, weights, score_fn: int = ROUTE_SOFTMAX, correction=None,
+              group_top: int = 1, renorm: bool = True) -> None:
+    """Per token: scores over all experts (`score_fn`: a softmax over the experts, or a sigmoid each); choice scores = scores +
+    `correction` (float32 [E], optional); the `keep` best of `groups` equal blocks of consecutive experts (a group counts as the
+    sum of its `group_top` largest choice scores: 1 = its best member); the `top` best experts of those by choice score. ids
+    int32 [T, top], weights float32 [T, top] = the chosen experts' scores, over their sum (+ 1e-20) with `renorm`."""
+    _dev(logits, ids, weights, correction)
     T, E = logits.shape
     _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "moe_route: logits must be float32 rows")
     _need(ids.dtype == torch.int32 and ids.is_contiguous() and ids.shape == (T, top) and weights.dtype == torch.float32 and
           weights.is_contiguous() and weights.shape == (T, top), "moe_route: ids int32 [T, top], weights float32 [T, top]")
-    call("tie_moe_route", logits.data_ptr(), logits.stride(0), T, E, top, groups, keep, ids.data_ptr(), weights.data_ptr(), _stream())
+    _need(correction is None or (correction.dtype == torch.float32 and correction.numel() == E and correction.is_contiguous()),
+          "moe_route: the correction must be float32 [experts]")
+    call("tie_moe_route", logits.data_ptr(), logits.stride(0), T, E, top, groups, keep, int(score_fn), _ptr(correction),
+         int(group_top), int(bool(renorm)), ids.data_ptr(), weights.data_ptr(), _stream())
 
 
 def moe_max_tiles(pairs: int, experts: int, block_m: int) -> int:
@@ -1078,3 +1086,158 @@ def gemm_grouped(a, w_blocks, out, N: int, K: int, meta, tile_group) -> None:
     bn = 256 if N >= 256 else 128
     call("tie_gemm_tc_grouped", dtype_code(out), a.data_ptr(), w_blocks.data_ptr(), out.data_ptr(), a.shape[0], N, K, a.stride(0),
          out.stride(0), bn, w_blocks.shape[1], meta.data_ptr(), tile_group.data_ptr(), _stream())
+
+
+# -- layers whose sublayers read the stream side by side, and what stands around them (csrc/parallel_layer.cu)
+
+def _delta_args(delta, x, what: str):
+    """(tensor pointer, partial sums pointer, stride, splits) of a sublayer's output: a tensor, a SplitSum or None."""
+    if delta is None:
+        return 0, 0, 0, 0
+    if isinstance(delta, SplitSum):
+        _need(delta.M == x.shape[0] and delta.N == x.shape[1], f"{what}: partial sums do not match x")
+        return 0, delta.partial.data_ptr(), delta.stride, delta.splits
+    _need(delta.shape == x.shape and delta.is_contiguous(), f"{what}: a delta must have x's shape")
+    return delta.data_ptr(), 0, 0, 0
+
+
+def pair_hash_add(x, table, tokens, positions, seq_of_row, query_start, state_slots, prev_state, buckets: int, mul_prev: int,
+                  mul_cur: int) -> None:
+    """x[t] += table[(prev * mul_prev + token * mul_cur) mod buckets], prev the token before t in its sequence; a sequence's
+    first token takes row `buckets`. `prev_state` int32 [slots] carries a request's last token from step to step."""
+    _dev(x, table, tokens, positions, seq_of_row, query_start, state_slots, prev_state)
+    T, D = x.shape
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "pair_hash_add: x must be float32 contiguous")
+    _need(table.dim() == 2 and table.shape == (buckets + 1, D) and table.is_contiguous(), "pair_hash_add: the table must be [buckets + 1, D]")
+    _need(prev_state.dtype == torch.int32 and prev_state.is_contiguous(), "pair_hash_add: the state must be int32")
+    for t in (tokens, positions, seq_of_row, query_start, state_slots):
+        _need(t.dtype == torch.int32, "pair_hash_add: index arrays must be int32")
+    call("tie_pair_hash_add", dtype_code(table), x.data_ptr(), table.data_ptr(), tokens.data_ptr(), positions.data_ptr(),
+         seq_of_row.data_ptr(), query_start.data_ptr(), state_slots.data_ptr(), prev_state.data_ptr(), int(buckets), int(mul_prev),
+         int(mul_cur), T, D, _stream())
+
+
+def add_row_vector(x, vec) -> None:
+    """x[t] += vec for every row; both float32."""
+    _dev(x, vec)
+    _need(x.dtype == torch.float32 and x.is_contiguous() and vec.dtype == torch.float32 and vec.is_contiguous() and
+          vec.numel() == x.shape[1], "add_row_vector: x float32 [T, D], vec float32 [D]")
+    call("tie_add_row_vector", x.data_ptr(), vec.data_ptr(), x.shape[0], x.shape[1], _stream())
+
+
+def group_norm_taps(x, groups: int, eps: float, w_a, out_a, w_b=None, out_b=None, taps_a=None, taps_b=None, ctx=None, unit=None,
+                    ring=None, delta=None, rows=None) -> None:
+    """u = x / rms over each of `groups` equal parts of a row; out_a = w_a * (u_t + sum_j taps_a[:, j] u_(t - taps + 1 + j)) and
+    likewise out_b (optional): a grouped RMS norm whose output passes h + conv(h), a causal convolution over time per channel.
+    With taps, `ctx` gives the step's index arrays, `ring` [slots, taps - 1, D] float32 the unit rows of earlier steps (by
+    position mod taps - 1) and `unit` [T, D] receives the rows that `parallel_finish` moves into the ring. Without taps it is the
+    grouped norm alone: `delta` (tensor or SplitSum) is added to x first and `rows` gathers (x is then left as it is)."""
+    T, D = x.shape
+    taps = 0 if taps_a is None else taps_a.shape[1]
+    _dev(x, w_a, w_b, out_a, out_b, taps_a, taps_b, unit, ring, rows)
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "group_norm_taps: x must be float32 contiguous")
+    n = out_a.shape[0]
+    _need(out_a.shape[1] == D and out_a.is_contiguous() and (out_b is None or (out_b.shape == out_a.shape and out_b.is_contiguous()
+                                                                              and out_b.dtype == out_a.dtype)),
+          "group_norm_taps: outputs must be [n, D] contiguous of one dtype")
+    for w in (w_a, w_b):
+        _need(w is None or (w.dtype == torch.float32 and w.numel() == D), "group_norm_taps: norm weights must be float32 [D]")
+    _need((w_b is None) == (out_b is None), "group_norm_taps: the second output needs a weight and a buffer")
+    for tw in (taps_a, taps_b):
+        _need(tw is None or (tw.dtype == torch.float32 and tw.shape == (D, taps) and tw.is_contiguous()),
+              "group_norm_taps: taps must be float32 [D, taps]")
+    if rows is None:
+        _need(n == T, "group_norm_taps: out must have x's rows")
+    else:
+        _need(rows.dtype == torch.int32 and rows.numel() == n, "group_norm_taps: rows must be int32 [n]")
+    dp, pp, ps, sp = _delta_args(delta, x, "group_norm_taps")
+    if delta is not None and not isinstance(delta, SplitSum):
+        _need(delta.dtype == out_a.dtype, "group_norm_taps: delta must have out's dtype")
+    if taps > 1:
+        _need(unit is not None and unit.dtype == torch.float32 and unit.shape == (T, D) and unit.is_contiguous() and
+              ring is not None and ring.dtype == torch.float32 and ring.dim() == 3 and ring.shape[1:] == (taps - 1, D) and
+              ring.is_contiguous(), "group_norm_taps: unit float32 [T, D], ring float32 [slots, taps - 1, D]")
+    idx = (ctx.seq_of_row, ctx.positions, ctx.query_start, ctx.context_lens, ctx.state_slots) if taps > 0 else (None,) * 5
+    call("tie_group_norm_taps", dtype_code(out_a), x.data_ptr(), dp, pp, ps, sp, _ptr(rows), n, D, int(groups), float(eps),
+         w_a.data_ptr(), _ptr(w_b), _ptr(taps_a), _ptr(taps_b), taps, out_a.data_ptr(), _ptr(out_b), _ptr(unit), _ptr(ring),
+         *(_ptr(t) for t in idx), _stream())
+
+
+def parallel_finish(x, mult: float, delta_a, delta_b, dtype, ctx=None, side=None, eps: float = 0.0, unit=None, ring=None) -> None:
+    """x += mult * (delta_a + delta_b) (each a tensor of `dtype`, a SplitSum or None), in float32. With `side` = (table
+    [vocab, n], gate [n, D], proj [D, n], norm float32 [D]) in `dtype`: g = gelu_tanh(gate x) * table[token], y = proj g,
+    x += mult * y / rms(y) * norm. With `ring`: the rows of `unit` that are a sequence's last ring.shape[1] positions after
+    this step go into the request's ring (what `group_norm_taps` left there)."""
+    T, D = x.shape
+    _dev(x, unit, ring)
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "parallel_finish: x must be float32 contiguous")
+    for d in (delta_a, delta_b):
+        _need(d is None or isinstance(d, SplitSum) or d.dtype == dtype, "parallel_finish: a delta tensor must be of the compute dtype")
+    a, b = _delta_args(delta_a, x, "parallel_finish"), _delta_args(delta_b, x, "parallel_finish")
+    n = 0
+    table = gate = proj = norm = None
+    if side is not None:
+        table, gate, proj, norm = side
+        _dev(table, gate, proj, norm)
+        n = gate.shape[0]
+        _need(table.dim() == 2 and table.shape[1] == n and gate.shape == (n, D) and proj.shape == (D, n) and
+              all(t.is_contiguous() and t.dtype == dtype for t in (table, gate, proj)) and norm.dtype == torch.float32 and
+              norm.numel() == D, "parallel_finish: side input tensors do not fit")
+    R = 0 if ring is None else ring.shape[1]
+    if R:
+        _need(ring.dtype == torch.float32 and ring.is_contiguous() and ring.shape[2] == D and unit is not None and
+              unit.dtype == torch.float32 and unit.shape == (T, D) and unit.is_contiguous(), "parallel_finish: ring float32 [slots, R, D], unit float32 [T, D]")
+    need_ctx = R > 0 or side is not None
+    call("tie_parallel_finish", F32 if dtype == torch.float32 else BF16, x.data_ptr(), T, D, float(mult), *a, *b,
+         ctx.tokens.data_ptr() if need_ctx else 0, _ptr(table), _ptr(gate), _ptr(proj), _ptr(norm), n, float(eps), _ptr(unit) if R else 0,
+         _ptr(ring) if R else 0, R, *((ctx.seq_of_row.data_ptr(), ctx.positions.data_ptr(), ctx.context_lens.data_ptr(),
+                                      ctx.state_slots.data_ptr()) if need_ctx else (0, 0, 0, 0)), _stream())
+
+
+# -- attention whose scores are mixed across heads, with a sink (csrc/attention_mixed.cu)
+
+def rope_pairs_unit_append(proj, q_off: int, k_off: int, v_off: int, inv_freq, unit: bool, eps: float, positions, slots, k_cache,
+                           v_cache, q_heads: int, kv_heads: int, dim: int, vdim: int) -> None:
+    """proj [T, ...] holds q, k and v of every token at columns q_off, k_off, v_off. The first 2 * len(inv_freq) dimensions of each
+    q and k head are turned in neighbouring pairs (2i, 2i+1) by position * inv_freq[i]; with `unit` each head is then divided by
+    its root mean square; q goes back in place, k and v into the cache planes at the token's slot."""
+    _dev(proj, inv_freq, positions, slots, k_cache, v_cache)
+    T = proj.shape[0]
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and q_off + q_heads * dim <= proj.shape[1] and k_off + kv_heads * dim <= proj.shape[1]
+          and v_off + kv_heads * vdim <= proj.shape[1], "rope_pairs_unit_append: q, k or v outside the projection")
+    _need(positions.dtype == torch.int32 and positions.numel() == T and slots.dtype == torch.int32 and slots.numel() == T,
+          "rope_pairs_unit_append: positions and slots must be int32 [T]")
+    _need(inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.is_contiguous()), "rope_pairs_unit_append: inv_freq must be float32")
+    _check_kv_planes(k_cache, v_cache, kv_heads, dim, vdim)
+    _need(k_cache.dtype == proj.dtype, "rope_pairs_unit_append: dtype differs from the cache's")
+    call("tie_rope_pairs_unit_append", dtype_code(proj), proj.data_ptr(), proj.stride(0), q_off, k_off, v_off, _ptr(inv_freq),
+         2 * inv_freq.numel() if inv_freq is not None else 0, int(bool(unit)), float(eps), positions.data_ptr(), slots.data_ptr(),
+         k_cache.data_ptr(), v_cache.data_ptr(), T, q_heads, kv_heads, dim, vdim, k_cache.shape[2], _stream())
+
+
+def attention_mixed(q, k_cache, v_cache, out, mix, ctx_arrays, rows: int, heads: int, kv_heads: int, dim: int, vdim: int, scale: float,
+                    sink: bool, seq_list=None, n_list: int = 0, split_keys: int = 0, max_splits: int = 0, scratch=None) -> None:
+    """Causal attention over the paged cache with scores mixed across heads (`mix` float32 [heads, heads] or None) and, with
+    `sink`, one more key of score 0 without a value in every softmax. `ctx_arrays` = (seq_of_row, query_start, context_lens,
+    block_tables). Rows [0, rows) each against the keys up to their own position; or, with `seq_list`, one row per listed
+    sequence with its keys in splits of `split_keys` that are merged in split order (scratch:
+    attention_split_scratch_floats(n_list, heads, vdim, max_splits) floats)."""
+    seq_of_row, query_start, context_lens, block_tables = ctx_arrays
+    _dev(q, k_cache, v_cache, out, mix, seq_of_row, query_start, context_lens, block_tables, seq_list, scratch)
+    _attn_common_dv(q, k_cache, v_cache, out, query_start, context_lens, block_tables, heads, kv_heads, dim, vdim)
+    _need(mix is None or (mix.dtype == torch.float32 and mix.shape == (heads, heads) and mix.is_contiguous()),
+          "attention_mixed: mix must be float32 [heads, heads]")
+    split = seq_list is not None
+    if split:
+        _need(seq_list.dtype == torch.int32 and seq_list.numel() >= n_list, "attention_mixed: seq_list must be int32 [n_list]")
+        _need(scratch is not None and scratch.dtype == torch.float32 and
+              scratch.numel() >= attention_split_scratch_floats(n_list, heads, vdim, max_splits), "attention_mixed: scratch too small")
+    else:
+        _need(seq_of_row.dtype == torch.int32 and seq_of_row.numel() >= rows and rows <= q.shape[0], "attention_mixed: seq_of_row must be int32 [T]")
+    call("tie_attention_mixed", dtype_code(q), q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+         _ptr(mix), seq_of_row.data_ptr(), query_start.data_ptr(), context_lens.data_ptr(), block_tables.data_ptr(),
+         block_tables.shape[1], rows, heads, kv_heads, dim, vdim, k_cache.shape[2], float(scale), int(bool(sink)),
+         _ptr(seq_list) if split else 0, n_list, split_keys, max_splits, _ptr(scratch) if split else 0, _stream())
+    if split and n_list > 0:
+        call("tie_attention_merge", dtype_code(out), out.data_ptr(), query_start.data_ptr(), context_lens.data_ptr(), heads, vdim,
+             0, seq_list.data_ptr(), n_list, split_keys, max_splits, scratch.data_ptr(), _stream())

@@ -62,13 +62,19 @@ _SIGNATURES = {
     "tie_attention_latent_split": [P, L, P, P, P, P, I, I, I, I, I, I, F, P, I, I, I, P, P],
     "tie_add_concat": [I, P, P, P, L, I, P, P, I, I, P],
     "tie_glu_biased": [I, P, P, P, P, I, I, I, I, P],
-    "tie_moe_route": [P, L, I, I, I, I, I, P, P, P],
+    "tie_moe_route": [P, L, I, I, I, I, I, I, P, I, I, P, P, P],
     "tie_moe_align": [P, I, I, I, P, P, P, P],
     "tie_moe_gemm": [I, I, I, P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, I, P],
     "tie_moe_gather": [I, P, L, P, P, I, I, P, I, I, P],
     "tie_moe_combine": [I, P, P, P, I, I, P, P, L, I, I, P],
     "tie_gemm_heads_mma": [P, L, I, P, P, L, I, I, I, I, I, P],
     "tie_gemm_tc_grouped": [I, P, P, P, I, I, I, L, L, I, I, P, P, P],
+    "tie_pair_hash_add": [I, P, P, P, P, P, P, P, P, I, L, L, I, I, P],
+    "tie_add_row_vector": [P, P, I, I, P],
+    "tie_group_norm_taps": [I, P, P, P, L, I, P, I, I, I, F, P, P, P, P, I, P, P, P, P, P, P, P, P, P, P],
+    "tie_parallel_finish": [I, P, I, I, F, P, P, L, I, P, P, L, I, P, P, P, P, P, I, F, P, P, I, P, P, P, P, P],
+    "tie_rope_pairs_unit_append": [I, P, L, I, I, I, P, I, I, F, P, P, P, P, I, I, I, I, I, I, P],
+    "tie_attention_mixed": [I, P, L, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P, I, I, I, P, P],
 }
 
 

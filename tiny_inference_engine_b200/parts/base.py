@@ -120,6 +120,15 @@ class Embedding(Part):
         """tokens int32 [T] -> x float32 [T, D] (written in place)."""
         raise NotImplementedError
 
+    def state_need(self) -> StateNeed | None:
+        """Per-request state of the embedding itself (one that looks at the token before, for instance)."""
+        return None
+
+    def forward_step(self, ctx, x: torch.Tensor, state) -> None:
+        """The call the model makes: the whole step (`ctx.tokens`, positions, sequences, state slots) and the
+        embedding's [slots, ...] state tensor (None without `state_need`). Called once a step."""
+        self.forward(ctx.tokens, x)
+
 
 class OutputHead(Part):
     """The rows that reached the final norm to float32 logits. Built with `embedding=` the model's embedding
@@ -142,6 +151,15 @@ class StreamInput(Part):
 
 class Block(Part):
     """The arrangement of mixer, feed-forward and their norms in one layer."""
+
+    # A block with state of its own (beside or instead of its mixer's) says so here: `state_need` is what a run entry
+    # of this layer keeps per request, `state_part()` the part whose `graph_safe` decides whether decode steps of the
+    # model may be captured as graphs. The default hands both questions to the mixer.
+    def state_need(self) -> StateNeed | None:
+        return self.mixer.state_need()
+
+    def state_part(self):
+        return self.mixer
 
     def forward(self, x: torch.Tensor, pending, ctx, cache, state):
         """x: float32 residual stream [T, D]; pending: a delta not yet added to x (or None).

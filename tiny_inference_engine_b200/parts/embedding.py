@@ -51,6 +51,43 @@ class NormedTokenEmbedding(TokenEmbedding):
         self.norm.rows(x, x)            # float32 rows, in place
 
 
+class PairHashEmbedding(TokenEmbedding):
+    """x[t] = table[id] + pairs[row]: a second table is indexed by a hash of the pair (previous token, token),
+    row = (prev * mul_prev + id * mul_cur) mod buckets; a sequence's first token takes the table's last row (`buckets`). The sum is
+    float32. The previous token of a request is per-request state (one int32 in its state slot), so that a prompt may be cut
+    anywhere. params beside `TokenEmbedding`'s: `pairs` = {"name", "buckets", "mul_prev", "mul_cur"}."""
+
+    def __init__(self, spec, dtype, prefix: str = ""):
+        super().__init__(spec, dtype, prefix)
+        pairs = spec["pairs"]
+        self.pairs_name = pairs["name"]
+        self.buckets, self.mul_prev, self.mul_cur = int(pairs["buckets"]), int(pairs["mul_prev"]), int(pairs["mul_cur"])
+        if self.buckets <= 0:
+            raise InvalidArgument(f"a pair table needs a positive number of buckets, got {self.buckets}")
+        self.pairs = None
+
+    def needs(self):
+        return {**super().needs(), self.pairs_name: TensorNeed((self.buckets + 1, self.hidden))}
+
+    def bind(self, get):
+        super().bind(get)
+        self.pairs = to_compute(get(self.pairs_name), self.dtype).contiguous()
+
+    def state_need(self):
+        from .base import StateNeed
+        return StateNeed((), torch.int32)
+
+    def forward(self, tokens, x):
+        raise InvalidArgument("this embedding reads the token before each token: it is called with the step (`forward_step`)")
+
+    def forward_step(self, ctx, x, state):
+        if state is None:
+            raise InvalidArgument("the pair-hash embedding keeps a request's last token in a state slot: none was given")
+        ops.embed(self.table, ctx.tokens, x)
+        ops.pair_hash_add(x, self.pairs, ctx.tokens, ctx.positions, ctx.seq_of_row, ctx.query_start, ctx.state_slots, state,
+                          self.buckets, self.mul_prev, self.mul_cur)
+
+
 class LMHead(OutputHead):
     def __init__(self, spec, dtype, embedding: TokenEmbedding | None = None, prefix: str = ""):
         self.name = spec["name"]
@@ -82,4 +119,5 @@ class LMHead(OutputHead):
 
 register_part("embedding", "token_embedding", TokenEmbedding, replace=True)
 register_part("embedding", "normed_token_embedding", NormedTokenEmbedding, replace=True)
+register_part("embedding", "pair_hash_embedding", PairHashEmbedding, replace=True)
 register_part("head", "lm_head", LMHead, replace=True)

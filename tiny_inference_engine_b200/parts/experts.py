@@ -1,9 +1,11 @@
 """A feed-forward of many small experts of which each token uses a few.
 
-    s      = softmax(h Wr^T) over all experts                      float32
-    chosen = the `top` experts with the largest s among the experts of the `group_keep` best of `group_count` equal
-             blocks of consecutive experts (a block's score is its best member's; ties go to the lower index)
-    weight = s[chosen] / (sum of s[chosen] + 1e-20)
+    s      = softmax(h Wr^T) over all experts, or sigmoid(h Wr^T) each (`score`: "softmax" | "sigmoid")   float32
+    c      = s + correction                                         (`correction`: a tensor `<prefix>correction` [experts]; else c = s)
+    chosen = the `top` experts with the largest c among the experts of the `group_keep` best of `group_count` equal
+             blocks of consecutive experts (a block's score is the sum of its `group_top` largest c, 1: its best
+             member's; ties go to the lower index; experts of other blocks count as minus infinity)
+    weight = s[chosen] / (sum of s[chosen] + 1e-20), or s[chosen] as it is (`renorm` false)
     out    = sum over chosen of weight * expert(h)
     expert = down(g * sigmoid(slope * g) * (u + up_shift)),  g = min(gate(h), limit), u = clamp(up(h), -limit, limit)
 
@@ -13,7 +15,7 @@ and two grouped products run over that list, the clamped unit between them. The 
 weight * result as float32 partial sums [top, tokens, hidden], which the block's next residual add sums in order:
 the weighted sum over experts happens in float32 in the residual add itself. What a token computes depends on its
 own experts only, never on what else is in the step. params: `hidden_size`, `intermediate_size`, `num_experts`, `top`,
-`group_count`, `group_keep`, `limit`, `slope`, `up_shift`; tensors `<prefix>router` and `<prefix>e<i>.gate|up|down`.
+`group_count`, `group_keep`, `group_top`, `score`, `correction`, `renorm`, `limit`, `slope`, `up_shift`; tensors `<prefix>router` and `<prefix>e<i>.gate|up|down`.
 """
 from __future__ import annotations
 
@@ -38,6 +40,13 @@ class RoutedExperts(FeedForward):
         self.experts, self.top = int(p["num_experts"]), int(p["top"])
         self.group_count, self.group_keep = int(p.get("group_count", 1)), int(p.get("group_keep", 1))
         self.limit, self.slope, self.up_shift = float(p["limit"]), float(p.get("slope", 1.0)), float(p.get("up_shift", 0.0))
+        score = p.get("score", "softmax")
+        if score not in ("softmax", "sigmoid"):
+            raise InvalidArgument(f"experts: a router scores by 'softmax' or 'sigmoid', got '{score}'")
+        self.score_fn = ops.ROUTE_SIGMOID if score == "sigmoid" else ops.ROUTE_SOFTMAX
+        self.group_top, self.renorm = int(p.get("group_top", 1)), bool(p.get("renorm", True))
+        self.has_correction = bool(p.get("correction", False))
+        self.correction = None
         E, G = self.experts, self.group_count
         if min(E, self.top, G, self.group_keep, self.inter) <= 0 or E % G or self.group_keep > G or \
                 self.top > self.group_keep * (E // G) or self.top > 32:
@@ -50,6 +59,8 @@ class RoutedExperts(FeedForward):
 
     def needs(self):
         n = {self.prefix + "router": TensorNeed((self.experts, self.hidden))}
+        if self.has_correction:
+            n[self.prefix + "correction"] = TensorNeed((self.experts,))
         for e in range(self.experts):
             n[self._expert(e, "gate")] = TensorNeed((self.inter, self.hidden))
             n[self._expert(e, "up")] = TensorNeed((self.inter, self.hidden))
@@ -65,6 +76,8 @@ class RoutedExperts(FeedForward):
         self.router = ops.bound_gemm(padded, split_many=False, pack=False)     # row-major: few tokens read it on the CUDA cores
         self.w_router = self.router.w
         self.router_rows = rows
+        if self.has_correction:
+            self.correction = get(self.prefix + "correction").to(torch.float32).contiguous()
         # [experts, 2 * inter, hidden]: an expert's gate rows, then its up rows; [experts, hidden, inter]
         w_gate_up = torch.stack([torch.cat([to_compute(get(self._expert(e, "gate")), self.dtype),
                                             to_compute(get(self._expert(e, "up")), self.dtype)], dim=0) for e in range(E)]).contiguous()
@@ -86,7 +99,8 @@ class RoutedExperts(FeedForward):
             self.router(h, logits)
         ids = ctx.ws.rows("moe.ids", T, top, torch.int32)
         weights = ctx.ws.rows("moe.weights", T, top, torch.float32)
-        ops.moe_route(logits[:, :E], top, self.group_count, self.group_keep, ids, weights)
+        ops.moe_route(logits[:, :E], top, self.group_count, self.group_keep, ids, weights, score_fn=self.score_fn,
+                      correction=self.correction, group_top=self.group_top, renorm=self.renorm)
         pairs = T * top
         few = pairs <= 8 * E      # an expert has a few rows: a warp per output column streams its weights once
         if self.in_blocks:

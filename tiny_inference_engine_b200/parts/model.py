@@ -73,7 +73,15 @@ class Model:
         return [self.layers[e.layer].mixer.cache_need() if e.cache_of is None else None for e in self.spec.run_order]
 
     def state_needs(self) -> list[StateNeed | None]:
-        return [self.layers[e.layer].mixer.state_need() for e in self.spec.run_order]
+        """Per run entry: the fixed-size state its layer keeps per request (the block's answer: its mixer's, or its own)."""
+        def need(block):
+            return block.state_need() if hasattr(block, "state_need") else block.mixer.state_need()
+        return [need(self.layers[e.layer]) for e in self.spec.run_order]
+
+    def extra_state_needs(self) -> dict[str, StateNeed]:
+        """Per-request state that belongs to no run entry, by name: the embedding's."""
+        need = self.embedding.state_need() if hasattr(self.embedding, "state_need") else None
+        return {} if need is None else {"embedding": need}
 
     def load(self, source: TensorSource, device="cuda") -> "Model":
         needs = self.needs()
@@ -112,11 +120,19 @@ class Model:
         T, D = ctx.T, self.spec.hidden_size
         ctx.ws_dtype = self.dtype
         x = ctx.ws.rows("model.x", T, D, torch.float32)
-        self.embedding.forward(ctx.tokens, x)
+        embed_state = states.extra("embedding") if states is not None and hasattr(states, "extra") else None
+        if hasattr(self.embedding, "forward_step"):
+            self.embedding.forward_step(ctx, x, embed_state)
+        else:
+            self.embedding.forward(ctx.tokens, x)
         origin = None
-        if self.stream_inputs:          # parts that mix the embedding back in later read it from a buffer of its own
+        if any(getattr(p, "reads_origin", True) for p in self._stream_input_parts):
+            # parts that mix the embedding back in later read it from a buffer of its own
             origin = ctx.ws.rows("model.origin", T, D, torch.float32)
-            self.embedding.forward(ctx.tokens, origin)
+            if embed_state is not None:
+                origin.copy_(x)         # an embedding with state is run once a step
+            else:
+                self.embedding.forward(ctx.tokens, origin)
         pending = None
         order = self.spec.run_order
 

@@ -50,3 +50,41 @@ class RMSNormOnePlus(RMSNorm):
 
 
 register_part("norm", "rmsnorm_one_plus", RMSNormOnePlus, replace=True)
+
+
+class GroupedRMSNorm(Norm):
+    """RMS norm in groups: a row is split into `groups` equal consecutive parts, each divided by its own
+    sqrt(mean(part^2) + eps), and the whole multiplied by the weight. With one group it is `RMSNorm`'s formula, through
+    the kernel that also serves layers whose sublayers read one stream side by side (`parallel_taps`)."""
+    launches_only = True
+    takes_split_sum = True
+
+    def __init__(self, spec, dtype, prefix: str = ""):
+        self.name = prefix + spec["name"]
+        self.size = int(spec["size"])
+        self.eps = float(spec["eps"])
+        self.groups = int(spec.params.get("groups", 1))
+        if self.groups <= 0 or self.size % self.groups:
+            from ..errors import InvalidArgument
+            raise InvalidArgument(f"a norm over {self.size} columns cannot have {self.groups} equal groups")
+        self.dtype = dtype
+        self.weight = None
+
+    def needs(self):
+        return {self.name: TensorNeed((self.size,), "norm")}
+
+    def bind(self, get):
+        self.weight = get(self.name).to(torch.float32).contiguous()
+
+    def add_norm(self, x, delta, out, rows=None):
+        if isinstance(delta, ops.NormedDelta):
+            raise NotImplementedError("a grouped norm takes a plain delta or partial sums, not one that still has a norm to pass")
+        ops.group_norm_taps(x, self.groups, self.eps, self.weight, out, delta=delta, rows=rows)
+
+    def rows(self, x, out):
+        if x.dtype != torch.float32 or not x.is_contiguous():
+            raise NotImplementedError("a grouped norm over other views than contiguous float32 rows")
+        ops.group_norm_taps(x, self.groups, self.eps, self.weight, out)
+
+
+register_part("norm", "grouped_rmsnorm", GroupedRMSNorm, replace=True)

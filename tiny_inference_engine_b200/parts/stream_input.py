@@ -40,4 +40,30 @@ class ConcatProjection(StreamInput):
         return None
 
 
+class PassVector(StreamInput):
+    """x[t] += vectors[index]: one learned vector joins every row of the stream (float32) ahead of a pass over a span
+    of layers; `vectors` is [passes, hidden] and every pass names its own row. params: `name`, `index`, `passes`,
+    `hidden_size`."""
+    launches_only = True
+    reads_origin = False        # the model need not keep the embedding's output for it
+
+    def __init__(self, spec, dtype, prefix: str = ""):
+        self.name = prefix + spec["name"]
+        self.index, self.passes, self.hidden = int(spec["index"]), int(spec["passes"]), int(spec["hidden_size"])
+        self.vector = None
+
+    def needs(self):
+        return {self.name: TensorNeed((self.passes, self.hidden))}
+
+    def bind(self, get):
+        self.vector = get(self.name)[self.index].to(torch.float32).contiguous()
+
+    def forward(self, x, pending, origin, ctx):
+        if pending is not None:
+            raise NotImplementedError("pass_vector stands behind layers that leave the stream complete")
+        ops.add_row_vector(x, self.vector)
+        return None
+
+
 register_part("stream_input", "concat_projection", ConcatProjection, replace=True)
+register_part("stream_input", "pass_vector", PassVector, replace=True)
