@@ -149,12 +149,19 @@ def attention_mixer(h, w, p, mx, eps, positions):
     v = linear(h, w[p + "v"]).reshape(T, G, vdim)
     q = kept(unit_rms(rotate_pairs(q, positions, rot["dims"], rot["base"]), eps))
     k = kept(unit_rms(rotate_pairs(k, positions, rot["dims"], rot["base"]), eps))
-    per = H // G
-    raw = np.stack([q[:, hd] @ k[:, hd // per].T for hd in range(H)]) * mx["scale"]          # [H, T, T]
-    mixed = np.einsum("hg,gij->hij", f64(w[p + "talk"]), raw)
-    weights = sink_softmax(mixed)
-    out = np.stack([weights[hd] @ v[:, hd // per] for hd in range(H)], axis=1)                # [T, H, vdim]
+    out = attend(q, k, v, w[p + "talk"], mx["scale"])
     return linear(kept(out.reshape(T, H * vdim)), w[p + "o"])
+
+
+def attend(q, k, v, talk, scale):
+    """q [T, H, dim], k [T, G, dim], v [T, G, vdim] of one sequence -> [T, H, vdim]: scaled scores of every query head against
+    its key head, mixed across heads by `talk` [H, H], causal softmax with the sink, weighted values."""
+    q, k, v = f64(q), f64(k), f64(v)
+    H, per = q.shape[1], q.shape[1] // k.shape[1]
+    raw = np.stack([q[:, hd] @ k[:, hd // per].T for hd in range(H)]) * scale                 # [H, T, T]
+    mixed = np.einsum("hg,gij->hij", f64(talk), raw)
+    weights = sink_softmax(mixed)
+    return np.stack([weights[hd] @ v[:, hd // per] for hd in range(H)], axis=1)
 
 
 # --------------------------------------------------------------------------- experts
@@ -253,3 +260,96 @@ def generate(w, cfg, prompt, n):
     for _ in range(n):
         tokens.append(int(np.argmax(forward(w, cfg, tokens)[-1])))
     return tokens[len(prompt):]
+
+
+# --------------------------------------------------------------------------- small configurations and random weights
+
+def moe(ff=24, experts=8, top=2, groups=4, keep=2, limit=1.5):
+    return {"kind": "moe", "expert": {"ff": ff, "limit": limit},
+            "router": {"experts": experts, "top": top, "groups": {"count": groups, "keep": keep}}}
+
+
+def attention_layer(heads=4, kv_heads=2, dim=16, vdim=24, rot_dims=8, base=10000.0, scale=None, mlp="moe"):
+    mx = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale if scale is not None else dim ** -0.5}
+    if rot_dims is not None:
+        mx["rot"] = {"base": base, "dims": rot_dims}
+    return {"type": "attention", "mixer": mx, "mlp": moe() if mlp == "moe" else mlp}
+
+
+def make_config(layers, vocab=160, width=64, eps=1e-6, groups=2, mult=0.8, taps=3, side=6, bigram=(53, 5, 3), loop=None):
+    """`bigram` = (buckets, mul_prev, mul_cur) or None; `taps` 0 and `side` 0 leave those mechanisms out."""
+    cfg = {"architecture": "Lufatar", "vocab": vocab, "width": width, "norm": {"eps": eps, "groups": groups},
+           "residual_mult": mult, "layers": layers}
+    if taps:
+        cfg["canon"] = {"taps": taps}
+    if side:
+        cfg["token_side"] = {"dim": side}
+    if bigram is not None:
+        cfg["embedding"] = {"bigram": {"buckets": bigram[0], "mul_prev": bigram[1], "mul_cur": bigram[2]}}
+    if loop is not None:
+        cfg["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return cfg
+
+
+def tensor_shapes(cfg):
+    D, V, n = cfg["width"], cfg["vocab"], len(cfg["layers"])
+    s = {"embed": (V, D), "final.norm": (D,), "head": (V, D)}
+    bg = (cfg.get("embedding") or {}).get("bigram")
+    if bg:
+        s["bigram"] = (bg["buckets"] + 1, D)
+    if cfg.get("loop"):
+        s["loop.step"] = (cfg["loop"]["times"], D)
+    side = (cfg.get("token_side") or {}).get("dim", 0)
+    if side:
+        s["side.embed"] = (V, n * side)
+    taps = (cfg.get("canon") or {}).get("taps", 0)
+    for i, layer in enumerate(cfg["layers"]):
+        p, mx, mlp = f"l{i}.", layer["mixer"], layer.get("mlp")
+        H, G, dim, vdim = mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"]
+        s.update({p + "norm1": (D,), p + "mix.q": (H * dim, D), p + "mix.k": (G * dim, D), p + "mix.v": (G * vdim, D),
+                  p + "mix.talk": (H, H), p + "mix.o": (D, H * vdim)})
+        if taps:
+            s[p + "canon1"] = (D, taps)
+        if mlp is not None:
+            s[p + "norm2"] = (D,)
+            if taps:
+                s[p + "canon2"] = (D, taps)
+            E, ff = mlp["router"]["experts"], mlp["expert"]["ff"]
+            s[p + "mlp.router"], s[p + "mlp.correction"] = (E, D), (E,)
+            for e in range(E):
+                s.update({f"{p}mlp.e{e}.gate": (ff, D), f"{p}mlp.e{e}.up": (ff, D), f"{p}mlp.e{e}.down": (D, ff)})
+        if side:
+            s.update({p + "side.gate": (side, D), p + "side.proj": (D, side), p + "side.norm": (D,)})
+    return s
+
+
+def random_weights(cfg, seed, sharp=3.0, expert_gain=1.0):
+    """float32 weights that bfloat16 holds exactly (so that both dtypes load the same model). Matrices are N(0, 1/in); the
+    query and key projections are `sharp` times larger (queries and keys are normed to unit RMS, so the config's `scale`
+    decides how peaked attention is; `sharp` only keeps the products well above rounding). The head mix is the identity
+    plus noise, with clearly non-zero entries off the diagonal. `expert_gain` scales what the experts add to the stream (a
+    close routing call that 16-bit rounding decides the other way then stays within a 16-bit tolerance)."""
+    rng = np.random.default_rng(seed)
+    w = {}
+    for name, shape in tensor_shapes(cfg).items():
+        leaf = name.split(".")[-1]
+        if name in ("embed", "bigram", "side.embed", "loop.step"):
+            t = rng.standard_normal(shape) * (0.5 if name != "embed" else 1.0)
+        elif leaf in ("norm1", "norm2", "norm"):
+            t = 1.0 + rng.standard_normal(shape) * 0.1
+        elif leaf in ("canon1", "canon2"):
+            t = rng.standard_normal(shape) * 0.4
+        elif leaf == "talk":
+            t = np.eye(shape[0]) + rng.standard_normal(shape) * 0.3
+        elif leaf == "correction":
+            t = rng.standard_normal(shape) * 0.3
+        else:
+            t = rng.standard_normal(shape) / np.sqrt(shape[-1])
+            if leaf in ("q", "k") and ".mix." in name:
+                t = t * sharp
+            if leaf == "router":
+                t = t * 4.0
+            if leaf == "down" and ".mlp.e" in name:
+                t = t * expert_gain
+        w[name] = round_bf16(np.asarray(t, dtype=np.float32))
+    return w

@@ -76,18 +76,21 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
   const int per = experts / groups;
   if (keep < groups) {
     for (int g = lane; g < groups; g += 32) {
-      // the sum of the group's `group_top` largest choice scores: pick the largest that is left, that often
-      float total = 0.0f;
-      unsigned long long taken = 0ull;        // members picked so far (the launcher allows group_top > 1 for up to 64 members)
+      // the sum of the group's `group_top` largest choice scores: the members in the order (score down, index up), each pick
+      // the first one after the pick before
+      float total = 0.0f, prev_v = INFINITY;
+      int prev_i = -1;
       for (int k = 0; k < min(group_top, per); ++k) {
         float b = -INFINITY;
         int bi = -1;
         for (int e = 0; e < per; ++e) {
-          const bool used = k > 0 && ((taken >> e) & 1ull) != 0ull;
-          if (!used && (bi < 0 || work[g * per + e] > b)) b = work[g * per + e], bi = e;
+          const float v = work[g * per + e];
+          const bool after = v < prev_v || (v == prev_v && e > prev_i) || (k == 0);
+          if (after && (bi < 0 || v > b)) b = v, bi = e;
         }
+        if (bi < 0) break;                    // nothing comparable is left (NaN)
         total += b;
-        taken |= 1ull << (bi & 63);
+        prev_v = b, prev_i = bi;
       }
       gbest[g] = total;
       gsel[g] = 0;
@@ -407,7 +410,6 @@ TIE_API int tie_moe_route(const float* logits, long long ld_logits, int tokens, 
                           cudaStream_t s) {
   TIE_REQUIRE((score_fn == 0 || score_fn == 1) && group_top >= 1, "moe_route: score function %d, %d members a group's score",
               score_fn, group_top);
-  TIE_REQUIRE(group_top == 1 || experts / (groups > 0 ? groups : 1) <= 64, "moe_route: groups of more than 64 experts count their best member only");
   TIE_REQUIRE(experts > 0 && top > 0 && top <= 32 && top <= experts && groups > 0 && experts % groups == 0 && keep > 0 &&
                   keep <= groups && top <= keep * (experts / groups),
               "moe_route: bad routing experts=%d top=%d (at most 32) groups=%d keep=%d", experts, top, groups, keep);

@@ -1241,3 +1241,22 @@ def attention_mixed(q, k_cache, v_cache, out, mix, ctx_arrays, rows: int, heads:
     if split and n_list > 0:
         call("tie_attention_merge", dtype_code(out), out.data_ptr(), query_start.data_ptr(), context_lens.data_ptr(), heads, vdim,
              0, seq_list.data_ptr(), n_list, split_keys, max_splits, scratch.data_ptr(), _stream())
+
+
+def attention_mixed_tc_takes(heads: int, kv_heads: int, dim: int, vdim: int) -> bool:
+    """Whether `attention_mixed_tc` serves this geometry (bfloat16 only); the CUDA-core kernel serves every geometry."""
+    return bool(library.library().tie_attention_mixed_tc_takes(int(heads), int(kv_heads), int(dim), int(vdim)))
+
+
+def attention_mixed_tc(q, k_cache, v_cache, out, mix, query_start, context_lens, block_tables, n_seqs: int, max_queries: int,
+                       heads: int, kv_heads: int, dim: int, vdim: int, scale: float, sink: bool) -> None:
+    """`attention_mixed` for the rows of sequences 0 .. n_seqs-1, each bringing several tokens (at most `max_queries`), in
+    bfloat16 on the tensor cores."""
+    _dev(q, k_cache, v_cache, out, mix, query_start, context_lens, block_tables)
+    _attn_common_dv(q, k_cache, v_cache, out, query_start, context_lens, block_tables, heads, kv_heads, dim, vdim)
+    _need(q.dtype == torch.bfloat16, "attention_mixed_tc: bfloat16 only")
+    _need(mix is None or (mix.dtype == torch.float32 and mix.shape == (heads, heads) and mix.is_contiguous()),
+          "attention_mixed_tc: mix must be float32 [heads, heads]")
+    call("tie_attention_mixed_tc", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _ptr(mix),
+         query_start.data_ptr(), context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], int(n_seqs),
+         int(max_queries), heads, kv_heads, dim, vdim, k_cache.shape[2], float(scale), int(bool(sink)), _stream())

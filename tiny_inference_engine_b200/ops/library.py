@@ -74,6 +74,7 @@ _SIGNATURES = {
     "tie_group_norm_taps": [I, P, P, P, L, I, P, I, I, I, F, P, P, P, P, I, P, P, P, P, P, P, P, P, P, P],
     "tie_parallel_finish": [I, P, I, I, F, P, P, L, I, P, P, L, I, P, P, P, P, P, I, F, P, P, I, P, P, P, P, P],
     "tie_rope_pairs_unit_append": [I, P, L, I, I, I, P, I, I, F, P, P, P, P, I, I, I, I, I, I, P],
+    "tie_attention_mixed_tc": [P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
     "tie_attention_mixed": [I, P, L, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P, I, I, I, P, P],
 }
 
@@ -112,6 +113,8 @@ def library() -> ctypes.CDLL:
         lib.tie_gemm_tc2_pairs.argtypes = []
         lib.tie_attention_latent_mma_takes.restype = c_int
         lib.tie_attention_latent_mma_takes.argtypes = [c_int, c_int]
+        lib.tie_attention_mixed_tc_takes.restype = c_int
+        lib.tie_attention_mixed_tc_takes.argtypes = [c_int, c_int, c_int, c_int]
         lib.tie_gemm_heads_mma_takes.restype = c_int
         lib.tie_gemm_heads_mma_takes.argtypes = [P, L, I, P, P, L, I, I, I]
         lib.tie_moe_max_tiles.restype = c_int

@@ -88,6 +88,7 @@ class HeadMixAttention(Mixer):
         if self.position is not None:
             self.position.bind(get)
         self._capacity = None
+        self._tensor_cores = None       # whether prompts of this geometry run on the tensor cores: asked at first use
 
     def cache_need(self):
         return CacheNeed("full", self.kv_heads, self.head_dim, 0, value_dim=0 if self.value_dim == self.head_dim else self.value_dim)
@@ -111,7 +112,13 @@ class HeadMixAttention(Mixer):
         q = proj[:, :self.q_dim]
         arrays = (ctx.seq_of_row, ctx.query_start, ctx.context_lens, g.block_tables)
         if ctx.multi_rows > 0:
-            ops.attention_mixed(q, cache.k, cache.v, attn, self.mix, arrays, ctx.multi_rows, H, G, Dk, Dv, self.scale, self.sink)
+            if self._tensor_cores is None:
+                self._tensor_cores = self.dtype == torch.bfloat16 and ops.attention_mixed_tc_takes(H, G, Dk, Dv)
+            if self._tensor_cores:
+                ops.attention_mixed_tc(q, cache.k, cache.v, attn, self.mix, ctx.query_start, ctx.context_lens, g.block_tables,
+                                       ctx.multi_seqs, ctx.multi_max_queries, H, G, Dk, Dv, self.scale, self.sink)
+            else:
+                ops.attention_mixed(q, cache.k, cache.v, attn, self.mix, arrays, ctx.multi_rows, H, G, Dk, Dv, self.scale, self.sink)
         if ctx.single_count > 0:
             # one block serves all heads of a split: enough splits to fill the SMs, none shorter than SPLIT_KEYS
             longest = ctx.single_max_context
