@@ -314,7 +314,7 @@ def test_a_key_far_back_at_a_page_border_or_one_past_the_query(dtype, page):
             assert np.abs(got - want[pos]).max() <= tol * np.abs(want).max(), f"decoded token at {pos}, splits of {split_keys}"
 
 
-@pytest.mark.parametrize("geometry", [(4, 2, 128, 64), (2, 1, 64, 64), (8, 2, 64, 128), (3, 3, 128, 128), (12, 4, 64, 64), (16, 16, 64, 64),
+@pytest.mark.parametrize("geometry", [(4, 2, 128, 64), (2, 1, 64, 64), (8, 2, 64, 128), (3, 3, 128, 128), (12, 4, 64, 64), (16, 4, 64, 64),
                                       (1, 1, 64, 128), (6, 2, 128, 128)])
 @pytest.mark.parametrize("page", [16, 64])
 def test_prompt_portions_on_the_tensor_cores(geometry, page):
@@ -324,6 +324,7 @@ def test_prompt_portions_on_the_tensor_cores(geometry, page):
     from tiny_inference_engine_b200 import ops
     H, G, dim, vdim = geometry
     assert ops.attention_mixed_tc_takes(H, G, dim, vdim)
+    assert not ops.attention_mixed_tc_takes(16, 16, 128, 128) and not ops.attention_mixed_tc_takes(4, 2, 48, 64)     # the CUDA-core kernel's
     L = 700
     spans = [(652, 700), (263, 300)]                      # rows of the step: positions [a, b) of a sequence b long
     keys = [0, 1, page - 1, page, 63, 64, 65, 255, 256, 100, 651, 652]

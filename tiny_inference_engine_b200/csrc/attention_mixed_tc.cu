@@ -1,4 +1,4 @@
-// Prompt portions of the attention whose scores are mixed across heads (attention_mixed.cu has the contract), on the
+// Prompt portions of the attention whose scores are mixed across heads (attention_mixed.cu states what is computed), on the
 // tensor cores: bfloat16 queries, keys and values, float accumulation, mma.sync m16n8k16.
 //
 // A head's weights need every head's scores, so one CTA owns ALL heads of a block of query positions. A warp is one
