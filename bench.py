@@ -206,6 +206,19 @@ def misudra_config(width, layers, heads, kv_heads, ff, vocab, window=1024):
             "loop": {"start": layers // 2, "stop": layers, "times": 2}, "norm": {"eps": 1e-6}, "vocab": vocab, "width": width}
 
 
+def lufatar_config(width, layers, heads, kv_heads, ff, vocab, vdim=128):
+    """Head-mix attention with a sink and routed experts side by side in every layer, at the sizes of a Qwen3 layer: 4 of 32
+    experts of ff / 4 (as many active parameters as the dense feed-forward), grouped norms, input convolutions of 4 taps, a
+    token side input of 64 and a hashed pair table; the second half of the layers runs twice."""
+    layer = {"type": "attention", "mixer": {"dim": 128, "heads": heads, "kv_heads": kv_heads, "rot": {"base": 1000000.0, "dims": 64},
+                                            "scale": 128 ** -0.5, "vdim": vdim},
+             "mlp": {"expert": {"ff": ff // 4, "limit": 7.0}, "kind": "moe",
+                     "router": {"experts": 32, "groups": {"count": 8, "keep": 4}, "top": 4}}}
+    return {"architecture": "Lufatar", "layers": [layer] * layers, "loop": {"start": layers // 2, "stop": layers, "times": 2},
+            "norm": {"eps": 1e-6, "groups": 4}, "residual_mult": 0.7, "canon": {"taps": 4}, "token_side": {"dim": 64},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}}, "vocab": vocab, "width": width}
+
+
 DESIGN_SIZES = {     # name: (width, layers, heads, kv heads, feed-forward, vocab)
     "2048x16": (2048, 16, 16, 8, 6144, 151936),
     "4096x8": (4096, 8, 32, 8, 12288, 151936),
@@ -228,7 +241,9 @@ def design_bench(args) -> dict:
         width, layers, heads, kv_heads, ff, vocab = DESIGN_SIZES[size]
         if args.layers:
             layers = args.layers
-        configs = {"misudra": misudra_config(width, layers * 2 // 3, heads, kv_heads, ff, vocab)} if args.design == "misudra" else {}
+        configs = {"misudra": misudra_config(width, layers * 2 // 3, heads, kv_heads, ff, vocab)} if args.design in ("misudra", "lufatar") else {}
+        if args.design == "lufatar":
+            configs = {"lufatar": lufatar_config(width, layers * 2 // 3, heads, kv_heads, ff, vocab, vdim=args.design_vdim), **configs}
         configs.update({"dugazen": dugazen_config(width, layers, heads, kv_heads, ff, vocab, vdim=args.design_vdim),
                    "qwen3": dict(QWEN3_8B, hidden_size=width, intermediate_size=ff, num_hidden_layers=layers,
                                  num_attention_heads=heads, num_key_value_heads=kv_heads, vocab_size=vocab)})
@@ -304,7 +319,9 @@ def design_bench(args) -> dict:
             gc.collect()
             torch.cuda.empty_cache()
         rows.append(row)
-    return {"design": args.design, "beside": ("dugazen and qwen3 at equal width, heads and feed-forward and as many layer runs "
+    return {"design": args.design, "beside": ("misudra, dugazen and qwen3 at equal width, heads and feed-forward and as many layer runs "
+                                              "(two thirds of the layers, the second half run twice)" if args.design == "lufatar" else
+                                              "dugazen and qwen3 at equal width, heads and feed-forward and as many layer runs "
                                               "(two thirds of the layers, the second half run twice)" if args.design == "misudra" else
                                               "qwen3 at equal width, layers, heads and feed-forward"), "dtype": "bf16",
             "data": "synthetic (random weights, uniform random token ids)", "prefill_tokens": T, "batch": B, "context": CTX,
@@ -331,11 +348,11 @@ def main() -> int:
     ap.add_argument("--profile", choices=["decode", "prefill", "mixed"], help="run two steps of one kind (mixed: 30 requests "
                     "decoding at context 2,048 beside a 482-token portion of a prompt, the serving default of 512 tokens a step), kernel by kernel, between "
                     "cudaProfilerStart/Stop (for ncu --profile-from-start off) and print no bench line")
-    ap.add_argument("--design", choices=["dugazen", "misudra"], help="prefill and decode throughput of that design beside Qwen3 at equal "
+    ap.add_argument("--design", choices=["dugazen", "misudra", "lufatar"], help="prefill and decode throughput of that design beside Qwen3 at equal "
                     "sizes (a line of its own; the default workload and its line stay as they are)")
     ap.add_argument("--design-size", choices=sorted(DESIGN_SIZES), help="--design: one size only")
     ap.add_argument("--design-vdim", type=int, default=128, help="--design: size of a value head (keys have 128)")
-    ap.add_argument("--design-only", choices=["dugazen", "misudra", "qwen3"], help="--design: one of the two models only")
+    ap.add_argument("--design-only", choices=["dugazen", "misudra", "lufatar", "qwen3"], help="--design: one of the two models only")
     args = ap.parse_args()
 
     if args.design:

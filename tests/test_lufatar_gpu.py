@@ -315,16 +315,17 @@ def test_a_key_far_back_at_a_page_border_or_one_past_the_query(dtype, page):
 
 
 @pytest.mark.parametrize("geometry", [(4, 2, 128, 64), (2, 1, 64, 64), (8, 2, 64, 128), (3, 3, 128, 128), (12, 4, 64, 64), (16, 4, 64, 64),
-                                      (1, 1, 64, 128), (6, 2, 128, 128)])
+                                      (1, 1, 64, 128), (6, 2, 128, 128), (16, 8, 128, 128), (32, 8, 128, 128), (16, 16, 128, 128),
+                                      (32, 1, 64, 64), (24, 2, 64, 128), (12, 2, 128, 64)])
 @pytest.mark.parametrize("page", [16, 64])
 def test_prompt_portions_on_the_tensor_cores(geometry, page):
-    """The bfloat16 kernel for portions: two sequences in one call, portions that start and end inside key tiles and pages,
-    queries that ask for single keys (far back, at borders, their own, the one after them), against the plain rule and against
-    the CUDA-core kernel."""
+    """The bfloat16 kernel: two sequences in one call, portions that start and end inside key tiles and pages, queries that
+    ask for single keys (far back, at borders, their own, the one after them), against the plain rule and against the
+    CUDA-core kernel; then single rows of two sequences with their keys in splits."""
     from tiny_inference_engine_b200 import ops
     H, G, dim, vdim = geometry
     assert ops.attention_mixed_tc_takes(H, G, dim, vdim)
-    assert not ops.attention_mixed_tc_takes(16, 16, 128, 128) and not ops.attention_mixed_tc_takes(4, 2, 48, 64)     # the CUDA-core kernel's
+    assert not ops.attention_mixed_tc_takes(32, 32, 128, 128) and not ops.attention_mixed_tc_takes(4, 2, 48, 64)     # the CUDA-core kernel's
     L = 700
     spans = [(652, 700), (263, 300)]                      # rows of the step: positions [a, b) of a sequence b long
     keys = [0, 1, page - 1, page, 63, 64, 65, 255, 256, 100, 651, 652]
@@ -349,6 +350,25 @@ def test_prompt_portions_on_the_tensor_cores(geometry, page):
         ops.attention_mixed_tc(qd, kc, vc, a, mix, i32(starts), i32(lens), tables, 2, 48, H, G, dim, vdim, scale, sink)
         ops.attention_mixed(qd, kc, vc, b, mix, (i32([0] * 48 + [1] * 37), i32(starts), i32(lens), tables), len(rows), H, G, dim, vdim, scale, sink)
         assert (a.float() - b.float()).abs().max().item() <= 1e-2 * np.abs(want).max(), f"sink {sink}, mix {mix is not None}"
+    # single rows: the last row of each sequence (one asks for key 651 ... of its own sequence), splits of 64 and of 256 keys
+    singles = [(699, 700), (299, 300), (663, 664), (275, 276)]          # (position, length)
+    for a_row, b_row in ((0, 1), (2, 3)):
+        pair = [singles[a_row], singles[b_row]]
+        qd1 = torch.from_numpy(q[[p for p, _ in pair]].reshape(2, H * dim)).to(torch.bfloat16).cuda()
+        lens1, starts1 = i32([n for _, n in pair]), i32([0, 1, 2])
+        for split_keys, sink in ((64, True), (256, True), (128, False)):
+            splits = -(-max(n for _, n in pair) // split_keys)
+            got1, simt1 = torch.zeros((2, H * vdim), dtype=torch.bfloat16, device="cuda"), torch.zeros((2, H * vdim), dtype=torch.bfloat16, device="cuda")
+            scratch = torch.zeros(ops.attention_split_scratch_floats(2, H, vdim, splits), dtype=torch.float32, device="cuda")
+            ops.attention_mixed_tc(qd1, kc, vc, got1, talk, starts1, lens1, tables, 2, 1, H, G, dim, vdim, scale, sink,
+                                   seq_list=i32([0, 1]), split_keys=split_keys, max_splits=splits, scratch=scratch)
+            scratch.zero_()
+            ops.attention_mixed(qd1, kc, vc, simt1, talk, (i32([0, 1]), starts1, lens1, tables), 0, H, G, dim, vdim, scale, sink,
+                                seq_list=i32([0, 1]), n_list=2, split_keys=split_keys, max_splits=splits, scratch=scratch)
+            assert (got1.float() - simt1.float()).abs().max().item() <= 1e-2 * np.abs(want).max(), f"single rows, splits of {split_keys}"
+            if sink:
+                g1 = got1.float().cpu().numpy().reshape(2, H, vdim)
+                assert np.abs(g1 - want[[p for p, _ in pair]]).max() <= 1e-2 * np.abs(want).max(), f"single rows against the plain rule, splits of {split_keys}"
 
 
 def test_the_sink_takes_weight_and_the_head_mix_moves_it():

@@ -193,59 +193,132 @@ struct FinishArgs {
   const int* state_slots;
 };
 
-template <typename T>
+// RB rows a block: the side input's weights are read once for all of them (a row's sums do not depend on RB).
+template <typename T, int RB>
 __global__ void __launch_bounds__(256) parallel_finish_kernel(FinishArgs a) {
   pdl_sync();
   extern __shared__ float smem[];
-  float* row = smem;                   // [D]
-  float* g = row + a.D;                // [side_dim]
-  float* scratch = g + a.side_dim;     // [33]
-  const int t = blockIdx.x, D = a.D;
+  const int D = a.D, S = a.side_dim;
+  float* row = smem;                   // [RB][D]: the summed rows, later the side input's y
+  float* g = row + RB * D;             // [RB][S]
+  float* scratch = g + RB * S;         // [33]
+  const int t0 = blockIdx.x * RB;
+  const int nr = min(RB, a.T - t0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  float* xr = a.x + static_cast<long long>(t) * D;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    const long long idx = static_cast<long long>(t) * D + d;
-    const float v = xr[d] + a.mult * (delta_at<T>(a.a, idx) + delta_at<T>(a.b, idx));
-    row[d] = v;
-    if (a.side_dim == 0) xr[d] = v;
+  constexpr int V = Vec16<T>::N;
+  for (int r = 0; r < nr; ++r) {
+    float* xr = a.x + static_cast<long long>(t0 + r) * D;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+      const long long idx = static_cast<long long>(t0 + r) * D + d;
+      const float v = xr[d] + a.mult * (delta_at<T>(a.a, idx) + delta_at<T>(a.b, idx));
+      row[r * D + d] = v;
+      xr[d] = v;
+    }
   }
-  if (a.side_dim > 0) {
+  if (S > 0) {
     __syncthreads();
-    const int tok = a.tokens[t];
-    for (int i = warp; i < a.side_dim; i += nwarps) {
-      const T* wr = static_cast<const T*>(a.side_gate) + static_cast<long long>(i) * D;
-      float dot = 0.0f;
-      for (int d = lane; d < D; d += 32) dot = fmaf(ld(wr + d), row[d], dot);
-      dot = warp_sum(dot);
-      if (lane == 0) g[i] = gelu_tanh_side(dot) * ld(static_cast<const T*>(a.side_table) + static_cast<long long>(tok) * a.side_dim + i);
+    const T* gate = static_cast<const T*>(a.side_gate);
+    const T* table = static_cast<const T*>(a.side_table);
+    const bool wide_d = D % V == 0, wide_s = S % V == 0;
+    for (int i = warp; i < S; i += nwarps) {
+      const T* wr = gate + static_cast<long long>(i) * D;
+      float dot[RB];
+#pragma unroll
+      for (int r = 0; r < RB; ++r) dot[r] = 0.0f;
+      if (wide_d) {
+        for (int d = lane * V; d < D; d += 32 * V) {
+          Vec16<T> w;
+          w.load(wr + d);
+#pragma unroll
+          for (int r = 0; r < RB; ++r) {
+            if (r < nr) {
+#pragma unroll
+              for (int e = 0; e < V; ++e) dot[r] = fmaf(w.v[e], row[r * D + d + e], dot[r]);
+            }
+          }
+        }
+      } else {
+        for (int d = lane; d < D; d += 32) {
+          const float w = ld(wr + d);
+#pragma unroll
+          for (int r = 0; r < RB; ++r)
+            if (r < nr) dot[r] = fmaf(w, row[r * D + d], dot[r]);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < RB; ++r) {
+        const float sum = warp_sum(dot[r]);
+        if (lane == 0 && r < nr) g[r * S + i] = gelu_tanh_side(sum) * ld(table + static_cast<long long>(a.tokens[t0 + r]) * S + i);
+      }
     }
     __syncthreads();
-    float ss = 0.0f;
-    // y is formed twice (for its norm, then for the sum): side_dim terms an element
+    const T* proj = static_cast<const T*>(a.side_proj);
+    float ss[RB];
+#pragma unroll
+    for (int r = 0; r < RB; ++r) ss[r] = 0.0f;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
-      const T* wr = static_cast<const T*>(a.side_proj) + static_cast<long long>(d) * a.side_dim;
-      float y = 0.0f;
-      for (int i = 0; i < a.side_dim; ++i) y = fmaf(ld(wr + i), g[i], y);
-      ss = fmaf(y, y, ss);
+      const T* wr = proj + static_cast<long long>(d) * S;
+      float y[RB];
+#pragma unroll
+      for (int r = 0; r < RB; ++r) y[r] = 0.0f;
+      if (wide_s) {
+        for (int i = 0; i < S; i += V) {
+          Vec16<T> w;
+          w.load(wr + i);
+#pragma unroll
+          for (int r = 0; r < RB; ++r) {
+            if (r < nr) {
+#pragma unroll
+              for (int e = 0; e < V; ++e) y[r] = fmaf(w.v[e], g[r * S + i + e], y[r]);
+            }
+          }
+        }
+      } else {
+        for (int i = 0; i < S; ++i) {
+          const float w = ld(wr + i);
+#pragma unroll
+          for (int r = 0; r < RB; ++r)
+            if (r < nr) y[r] = fmaf(w, g[r * S + i], y[r]);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < RB; ++r) {
+        if (r < nr) {
+          ss[r] = fmaf(y[r], y[r], ss[r]);
+          row[r * D + d] = y[r];        // this thread's own column: the summed row is in x already
+        }
+      }
     }
-    ss = block_sum(ss, scratch);
-    const float inv = 1.0f / sqrtf(ss / static_cast<float>(D) + a.eps);
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-      const T* wr = static_cast<const T*>(a.side_proj) + static_cast<long long>(d) * a.side_dim;
-      float y = 0.0f;
-      for (int i = 0; i < a.side_dim; ++i) y = fmaf(ld(wr + i), g[i], y);
-      xr[d] = row[d] + a.mult * (y * inv) * a.side_norm[d];
+#pragma unroll
+    for (int r = 0; r < RB; ++r) {
+      const float total = block_sum(ss[r], scratch);
+      if (r < nr) {
+        const float inv = 1.0f / sqrtf(total / static_cast<float>(D) + a.eps);
+        float* xr = a.x + static_cast<long long>(t0 + r) * D;
+        for (int d = threadIdx.x; d < D; d += blockDim.x) xr[d] += a.mult * (row[r * D + d] * inv) * a.side_norm[d];
+      }
     }
   }
   if (a.R > 0) {
-    const int s = a.seq_of_row[t];
-    const int pos = a.positions[t], slot = a.state_slots[s];
-    if (slot >= 0 && pos >= a.context_lens[s] - a.R) {
-      const float* src = a.unit + static_cast<long long>(t) * D;
-      float* dst = a.ring + (static_cast<long long>(slot) * a.R + pos % a.R) * D;
-      for (int d = threadIdx.x; d < D; d += blockDim.x) dst[d] = src[d];
+    for (int r = 0; r < nr; ++r) {
+      const int t = t0 + r;
+      const int s = a.seq_of_row[t];
+      const int pos = a.positions[t], slot = a.state_slots[s];
+      if (slot >= 0 && pos >= a.context_lens[s] - a.R) {
+        const float* src = a.unit + static_cast<long long>(t) * D;
+        float* dst = a.ring + (static_cast<long long>(slot) * a.R + pos % a.R) * D;
+        for (int d = threadIdx.x; d < D; d += blockDim.x) dst[d] = src[d];
+      }
     }
   }
+}
+
+template <typename T, int RB>
+static int launch_finish(const FinishArgs& a, cudaStream_t s) {
+  const size_t smem = (static_cast<size_t>(RB) * (a.D + a.side_dim) + 40) * sizeof(float);
+  if (smem > 48 * 1024) cudaFuncSetAttribute(parallel_finish_kernel<T, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  TIE_LAUNCH((parallel_finish_kernel<T, RB>), ceil_div(a.T, RB), 256, smem, s, a);
+  TIE_RETURN_LAUNCH("parallel_finish");
 }
 
 }  // namespace tie
@@ -343,17 +416,13 @@ TIE_API int tie_parallel_finish(int dtype, float* x, int rows, int dim, float mu
   a.side_dim = side_dim, a.eps = eps;
   a.unit = unit, a.ring = ring, a.R = ring_rows;
   a.seq_of_row = seq_of_row, a.positions = positions, a.context_lens = context_lens, a.state_slots = state_slots;
-  const size_t smem = (static_cast<size_t>(dim) + side_dim + 40) * sizeof(float);
-  TIE_REQUIRE(smem <= 200 * 1024, "parallel_finish: a row of %d columns does not fit shared memory", dim);
-  if (dtype == TIE_F32) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(parallel_finish_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    TIE_LAUNCH((parallel_finish_kernel<float>), rows, 256, smem, s, a);
-  } else if (dtype == TIE_BF16) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(parallel_finish_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    TIE_LAUNCH((parallel_finish_kernel<__nv_bfloat16>), rows, 256, smem, s, a);
-  } else {
-    set_error("parallel_finish: unknown dtype code %d", dtype);
-    return kBadArgument;
-  }
-  TIE_RETURN_LAUNCH("parallel_finish");
+  // four rows a block once that still fills the SMs twice over (and fits shared memory): the side input's weights are then
+  // read once for the four
+  const size_t one = (static_cast<size_t>(dim) + side_dim + 40) * sizeof(float), four = (4 * (static_cast<size_t>(dim) + side_dim) + 40) * sizeof(float);
+  TIE_REQUIRE(one <= 200 * 1024, "parallel_finish: a row of %d columns does not fit shared memory", dim);
+  const bool batch = side_dim > 0 && rows >= 4 * 2 * 148 && four <= 100 * 1024;
+  if (dtype == TIE_F32) return batch ? launch_finish<float, 4>(a, s) : launch_finish<float, 1>(a, s);
+  if (dtype == TIE_BF16) return batch ? launch_finish<__nv_bfloat16, 4>(a, s) : launch_finish<__nv_bfloat16, 1>(a, s);
+  set_error("parallel_finish: unknown dtype code %d", dtype);
+  return kBadArgument;
 }

@@ -1249,14 +1249,25 @@ def attention_mixed_tc_takes(heads: int, kv_heads: int, dim: int, vdim: int) -> 
 
 
 def attention_mixed_tc(q, k_cache, v_cache, out, mix, query_start, context_lens, block_tables, n_seqs: int, max_queries: int,
-                       heads: int, kv_heads: int, dim: int, vdim: int, scale: float, sink: bool) -> None:
-    """`attention_mixed` for the rows of sequences 0 .. n_seqs-1, each bringing several tokens (at most `max_queries`), in
-    bfloat16 on the tensor cores."""
-    _dev(q, k_cache, v_cache, out, mix, query_start, context_lens, block_tables)
+                       heads: int, kv_heads: int, dim: int, vdim: int, scale: float, sink: bool, seq_list=None, split_keys: int = 0,
+                       max_splits: int = 0, scratch=None) -> None:
+    """`attention_mixed` in bfloat16 on the tensor cores: for the rows of sequences 0 .. n_seqs-1, each bringing several tokens
+    (at most `max_queries`); or, with `seq_list` (int32 [n_seqs]), one row per listed sequence with its keys in splits of
+    `split_keys` (a multiple of 64) that are merged in split order (scratch as for `attention_mixed`)."""
+    _dev(q, k_cache, v_cache, out, mix, query_start, context_lens, block_tables, seq_list, scratch)
     _attn_common_dv(q, k_cache, v_cache, out, query_start, context_lens, block_tables, heads, kv_heads, dim, vdim)
     _need(q.dtype == torch.bfloat16, "attention_mixed_tc: bfloat16 only")
     _need(mix is None or (mix.dtype == torch.float32 and mix.shape == (heads, heads) and mix.is_contiguous()),
           "attention_mixed_tc: mix must be float32 [heads, heads]")
+    split = seq_list is not None
+    if split:
+        _need(seq_list.dtype == torch.int32 and seq_list.numel() >= n_seqs, "attention_mixed_tc: seq_list must be int32 [n_seqs]")
+        _need(scratch is not None and scratch.dtype == torch.float32 and
+              scratch.numel() >= attention_split_scratch_floats(n_seqs, heads, vdim, max_splits), "attention_mixed_tc: scratch too small")
     call("tie_attention_mixed_tc", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _ptr(mix),
          query_start.data_ptr(), context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], int(n_seqs),
-         int(max_queries), heads, kv_heads, dim, vdim, k_cache.shape[2], float(scale), int(bool(sink)), _stream())
+         int(max_queries), heads, kv_heads, dim, vdim, k_cache.shape[2], float(scale), int(bool(sink)),
+         _ptr(seq_list) if split else 0, int(split_keys), int(max_splits), _ptr(scratch) if split else 0, _stream())
+    if split and n_seqs > 0:
+        call("tie_attention_merge", dtype_code(out), out.data_ptr(), query_start.data_ptr(), context_lens.data_ptr(), heads, vdim,
+             0, seq_list.data_ptr(), n_seqs, split_keys, max_splits, scratch.data_ptr(), _stream())

@@ -111,9 +111,9 @@ class HeadMixAttention(Mixer):
         attn = ctx.ws.rows("hmattn.out", T, self.o_dim, self.dtype)
         q = proj[:, :self.q_dim]
         arrays = (ctx.seq_of_row, ctx.query_start, ctx.context_lens, g.block_tables)
+        if self._tensor_cores is None:
+            self._tensor_cores = self.dtype == torch.bfloat16 and ops.attention_mixed_tc_takes(H, G, Dk, Dv)
         if ctx.multi_rows > 0:
-            if self._tensor_cores is None:
-                self._tensor_cores = self.dtype == torch.bfloat16 and ops.attention_mixed_tc_takes(H, G, Dk, Dv)
             if self._tensor_cores:
                 ops.attention_mixed_tc(q, cache.k, cache.v, attn, self.mix, ctx.query_start, ctx.context_lens, g.block_tables,
                                        ctx.multi_seqs, ctx.multi_max_queries, H, G, Dk, Dv, self.scale, self.sink)
@@ -128,9 +128,14 @@ class HeadMixAttention(Mixer):
                 split_keys *= 2
             max_splits = max(1, math.ceil(longest / split_keys))
             scratch = ctx.ws.flat("hmattn.split", ops.attention_split_scratch_floats(ctx.max_seqs, H, Dv, MAX_SPLITS), torch.float32)
-            ops.attention_mixed(q, cache.k, cache.v, attn, self.mix, arrays, 0, H, G, Dk, Dv, self.scale, self.sink,
-                                seq_list=ctx.single_seqs, n_list=ctx.single_count, split_keys=split_keys, max_splits=max_splits,
-                                scratch=scratch)
+            if self._tensor_cores:
+                ops.attention_mixed_tc(q, cache.k, cache.v, attn, self.mix, ctx.query_start, ctx.context_lens, g.block_tables,
+                                       ctx.single_count, 1, H, G, Dk, Dv, self.scale, self.sink, seq_list=ctx.single_seqs,
+                                       split_keys=split_keys, max_splits=max_splits, scratch=scratch)
+            else:
+                ops.attention_mixed(q, cache.k, cache.v, attn, self.mix, arrays, 0, H, G, Dk, Dv, self.scale, self.sink,
+                                    seq_list=ctx.single_seqs, n_list=ctx.single_count, split_keys=split_keys, max_splits=max_splits,
+                                    scratch=scratch)
         out = ctx.ws.rows("mixer.out", T, self.hidden, self.dtype)
         if self._capacity is None:
             self._capacity = ops.partial_capacity(ctx.ws.max_rows, self.gemm_o.N, self.gemm_o.K)
