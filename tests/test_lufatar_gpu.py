@@ -371,6 +371,80 @@ def test_prompt_portions_on_the_tensor_cores(geometry, page):
                 assert np.abs(g1 - want[[p for p, _ in pair]]).max() <= 1e-2 * np.abs(want).max(), f"single rows against the plain rule, splits of {split_keys}"
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["mixed", "odd", "square"])
+def test_the_token_side_input_as_matrix_products(tmp_path, truth, name, dtype, monkeypatch):
+    """Steps of many rows take the side input as two matrix products between small kernels: the same logits, whole and in
+    portions (portions below the bound go the other way, in the same request)."""
+    from tiny_inference_engine_b200.parts import block
+    monkeypatch.setattr(block, "SIDE_PRODUCT_ROWS", 12)
+    cfg, page = CONFIGS[name]
+    w = plain.random_weights(cfg, 5, expert_gain=GAIN)
+    toks = tokens_of(cfg, 150, 2)
+    want = truth(name, toks)
+    hs = Harness(tmp_path, cfg, w, dtype, page=page, pages=256 // page * 2)
+    close(hs.whole("w", toks), want, dtype, f"{name} whole")
+    close(hs.in_portions("p", toks, [40, 3, 12, 1, 30, 11, 2]), want, dtype, f"{name} in portions")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(32, 2, 4), (36, 3, 2), (64, 1, 3), (24, 4, 1)])
+def test_grouped_norm_with_taps_in_tiles_of_rows(shape, dtype):
+    """The norm and input convolution kernel in tiles of one, five and eight rows: the same numbers to the bit, and the plain
+    rule's: two sequences in one step, one going on from its ring at a position that is no multiple of the ring's length,
+    one from its first token (zeros ahead of it), a third row block that starts inside a tile."""
+    from types import SimpleNamespace
+    from tiny_inference_engine_b200 import ops
+    D, groups, taps = shape
+    R = taps - 1
+    rng = np.random.default_rng(D)
+    spans = [(10, 21), (0, 13), (5, 7)]             # (first position, rows) of each sequence of the step; slots 2, 0, 1
+    slots = [2, 0, 1]
+    T = sum(n for _, n in spans)
+    x = rng.standard_normal((T, D)).astype(np.float32) * 3.0
+    ring = rng.standard_normal((3, max(R, 1), D)).astype(np.float32)
+    wa, wb = rng.standard_normal(D).astype(np.float32), rng.standard_normal(D).astype(np.float32)
+    ta, tb = rng.standard_normal((D, taps)).astype(np.float32), rng.standard_normal((D, taps)).astype(np.float32)
+    eps = 1e-5
+    xg = x.reshape(T, groups, D // groups).astype(np.float64)
+    unit = (xg / np.sqrt((xg * xg).mean(-1, keepdims=True) + eps)).reshape(T, D)
+    want_a, want_b = np.zeros((T, D)), np.zeros((T, D))
+    seq_of_row, positions, starts, t = [], [], [0], 0
+    for s, (p0, n) in enumerate(spans):
+        for i in range(n):
+            back = []                               # unit rows at positions p - taps + 1 .. p
+            for r in range(R, -1, -1):
+                p = p0 + i - r
+                back.append(unit[t + i - r] if i - r >= 0 else ring[slots[s], p % R].astype(np.float64) if p >= 0 else np.zeros(D))
+            conv_a = sum(ta[:, j] * back[j] for j in range(taps))
+            conv_b = sum(tb[:, j] * back[j] for j in range(taps))
+            want_a[t + i], want_b[t + i] = wa * (unit[t + i] + conv_a), wb * (unit[t + i] + conv_b)
+            seq_of_row.append(s), positions.append(p0 + i)
+        t += n
+        starts.append(t)
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device="cuda")
+    ctx = SimpleNamespace(seq_of_row=i32(seq_of_row), positions=i32(positions), query_start=i32(starts),
+                          context_lens=i32([p0 + n for p0, n in spans]), state_slots=i32(slots))
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    outs = []
+    for tile in (1, 5, 8):
+        oa, ob = torch.zeros((T, D), dtype=dtype, device="cuda"), torch.zeros((T, D), dtype=dtype, device="cuda")
+        left = torch.zeros((T, D), dtype=torch.float32, device="cuda")
+        ops.group_norm_taps(dev(x), groups, eps, dev(wa), oa, dev(wb), ob, dev(ta), dev(tb), ctx=ctx, unit=left if R else None,
+                            ring=dev(ring) if R else None, tile=tile)
+        outs.append((oa.float().cpu().numpy(), ob.float().cpu().numpy(), left.cpu().numpy()))
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert np.abs(outs[0][0] - want_a).max() <= tol * np.abs(want_a).max() and np.abs(outs[0][1] - want_b).max() <= tol * np.abs(want_b).max()
+    for o in outs[1:]:
+        assert all(np.array_equal(a, b) for a, b in zip(o, outs[0])), "a row's numbers depend on its tile"
+    if R:
+        t = 0
+        for p0, n in spans:                         # the rows that will be the ring: a sequence's last taps - 1 unit rows
+            for i in range(max(0, n - R), n):
+                assert np.abs(outs[0][2][t + i] - unit[t + i]).max() <= 1e-5
+            t += n
+
+
 def test_the_sink_takes_weight_and_the_head_mix_moves_it():
     """Without the sink the weights of a row sum to one; with it, to less: a query that matches no key gives almost nothing."""
     from tiny_inference_engine_b200 import ops
@@ -538,15 +612,15 @@ def test_configurations_drawn_at_random(tmp_path, seed, dtype):
         # a side input of one number is a sign function of it (y / rms(y)), of three nearly one: 16-bit noise flips it
         cfg["token_side"]["dim"] = 8
     w = plain.random_weights(cfg, 100 + seed, expert_gain=GAIN)
-    a, b = tokens_of(cfg, 83, seed), tokens_of(cfg, 31, 50 + seed)
+    a, b = tokens_of(cfg, 83, seed), tokens_of(cfg, 47, 50 + seed)
     want_a, want_b = reference(w, cfg, a), reference(w, cfg, b)
     hs = Harness(tmp_path, cfg, w, dtype, page=page, pages=-(-256 // page), slots=2)
     close(hs.whole("w", a), want_a, dtype, f"seed {seed} whole")
     rows = hs.step([("a", a[:40], range(40))])
     rows.update(hs.step([("a", a[40:42], [0, 1]), ("b", b[:17], range(17))]))            # a portion of two beside a prompt
-    rows.update(hs.step([("b", b[17:], range(14)), ("a", a[42:43], [0])], end=["b"]))    # a prompt's end beside one token
+    rows.update(hs.step([("b", b[17:], range(30)), ("a", a[42:43], [0])], end=["b"]))    # a prompt's end beside one token
     rows.update(hs.step([("a", a[43:70], range(27))]))
     for i in range(70, 83):
         rows.update(hs.step([("a", a[i:i + 1], [0])]))
     close(np.stack([rows[("a", i)] for i in range(83)]), want_a, dtype, f"seed {seed} in portions and decoded")
-    close(np.stack([rows[("b", i)] for i in range(31)]), want_b, dtype, f"seed {seed} the request beside it")
+    close(np.stack([rows[("b", i)] for i in range(47)]), want_b, dtype, f"seed {seed} the request beside it")

@@ -16,6 +16,10 @@
 //   parallel_finish   x += mult * (delta_a + delta_b) (tensors or float partial sums, added in order), then the token
 //                     side input: g = gelu_tanh(W_gate x) * table[token], y = W_proj g, x += mult * y / rms(y) * w;
 //                     then the ring update. Sums, norms and the stream in float.
+//   For many rows the side input's two products run as matrix products instead, between three small kernels:
+//   parallel_sum      x += mult * (delta_a + delta_b); copy = x in the storage type (the first product's input).
+//   side_gate_act     g = gelu_tanh(pre) * table[token] for pre = copy W_gate^T (float), in the storage type.
+//   side_finish       x += mult * y / rms(y) * w for y = g W_proj^T (float), then the ring update.
 #include <math.h>
 
 #include "common.cuh"
@@ -166,6 +170,113 @@ __global__ void __launch_bounds__(256) group_norm_taps_kernel(NormTapsArgs a) {
   }
 }
 
+__device__ __forceinline__ void store_vec(float* p, const float (&v)[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+__device__ __forceinline__ void store_vec(__nv_bfloat16* p, const float (&v)[4]) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+  *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+}
+__device__ __forceinline__ void store_vec(float* p, const float (&v)[1]) { p[0] = v[0]; }
+__device__ __forceinline__ void store_vec(__nv_bfloat16* p, const float (&v)[1]) { st(p, v[0]); }
+template <int W> __device__ __forceinline__ void load_vec(const float* p, float (&v)[W]) {
+  if constexpr (W == 4) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
+  } else {
+    v[0] = p[0];
+  }
+}
+
+// group_norm_taps with taps for `tile` consecutive rows a block: the norms of the tile's rows and of the taps - 1 rows
+// before it are computed once (a warp per row and group), then every row of the tile forms its outputs, W columns a
+// thread at a time. A row's numbers do not depend on the tile it falls into.
+template <typename T, int W>
+__global__ void __launch_bounds__(256) group_norm_taps_tile_kernel(NormTapsArgs a, int tile) {
+  pdl_sync();
+  extern __shared__ float smem[];
+  float* inv = smem;                       // [(tile + R) * groups], row t0 - R first
+  const int D = a.D, R = a.taps - 1, G = a.groups;
+  const int gsize = D / G;
+  const int t0 = blockIdx.x * tile;
+  const int nr = min(tile, a.n - t0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int item = warp; item < (nr + R) * G; item += nwarps) {
+    const int j = item / G, g = item - j * G;
+    const int t = t0 - R + j;
+    if (t < 0) continue;
+    const float* src = a.x + static_cast<long long>(t) * D + g * gsize;
+    float ss = 0.0f;
+    for (int d = lane * W; d < gsize; d += 32 * W) {
+      float v[W];
+      load_vec<W>(src + d, v);
+#pragma unroll
+      for (int e = 0; e < W; ++e) ss = fmaf(v[e], v[e], ss);
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) inv[item] = 1.0f / sqrtf(ss / static_cast<float>(gsize) + a.eps);
+  }
+  int* meta = reinterpret_cast<int*>(inv + (tile + R) * G);      // [tile][4]: position, the portion's first position, slot, keep
+  for (int j = threadIdx.x; j < nr; j += blockDim.x) {
+    const int t = t0 + j;
+    const int s = a.seq_of_row[t];
+    const int pos = a.positions[t];
+    meta[4 * j] = pos;
+    meta[4 * j + 1] = pos - (t - a.query_start[s]);
+    meta[4 * j + 2] = a.state_slots[s];
+    meta[4 * j + 3] = R > 0 && pos >= a.context_lens[s] - R;
+  }
+  __syncthreads();
+  const int per_row = D / W;
+  for (int item = threadIdx.x; item < nr * per_row; item += blockDim.x) {
+    const int j = item / per_row, d = (item - j * per_row) * W;
+    const int t = t0 + j;
+    const int pos = meta[4 * j], first = meta[4 * j + 1], slot = meta[4 * j + 2];
+    const bool keep = meta[4 * j + 3] != 0;
+    const float* xr = a.x + static_cast<long long>(t) * D;
+    const float* my_inv = inv + (j + R) * G;
+    {
+      const int g = d / gsize;
+      float u[kMaxTaps][W];
+      load_vec<W>(xr + d, u[0]);
+#pragma unroll
+      for (int e = 0; e < W; ++e) u[0][e] *= my_inv[g];
+#pragma unroll
+      for (int r = 1; r < kMaxTaps; ++r) {
+        if (r > R) break;
+        const int p = pos - r;
+#pragma unroll
+        for (int e = 0; e < W; ++e) u[r][e] = 0.0f;
+        if (p >= first) {
+          load_vec<W>(xr + d - static_cast<long long>(r) * D, u[r]);
+          const float scale = my_inv[g - r * G];
+#pragma unroll
+          for (int e = 0; e < W; ++e) u[r][e] *= scale;
+        } else if (p >= 0 && slot >= 0) {
+          load_vec<W>(a.ring + (static_cast<long long>(slot) * R + p % R) * D + d, u[r]);
+        }
+      }
+      float oa[W], ob[W];
+#pragma unroll
+      for (int e = 0; e < W; ++e) {
+        float sa = u[0][e], sb = u[0][e];
+        const float* ta = a.taps_a + static_cast<long long>(d + e) * a.taps;
+        const float* tb = a.w_b != nullptr ? a.taps_b + static_cast<long long>(d + e) * a.taps : ta;
+#pragma unroll
+        for (int r = kMaxTaps - 1; r >= 0; --r) {       // tap taps - 1 - r reads the row r back; the oldest row first
+          if (r <= R) {
+            sa = fmaf(ta[R - r], u[r][e], sa);
+            if (a.w_b != nullptr) sb = fmaf(tb[R - r], u[r][e], sb);
+          }
+        }
+        oa[e] = a.w_a[d + e] * sa;
+        ob[e] = a.w_b != nullptr ? a.w_b[d + e] * sb : 0.0f;
+      }
+      store_vec(static_cast<T*>(a.out_a) + static_cast<long long>(t) * D + d, oa);
+      if (a.w_b != nullptr) store_vec(static_cast<T*>(a.out_b) + static_cast<long long>(t) * D + d, ob);
+      if (keep) store_vec(a.unit + static_cast<long long>(t) * D + d, u[0]);
+    }
+  }
+}
+
 __device__ __forceinline__ float gelu_tanh_side(float z) {
   return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
@@ -193,7 +304,7 @@ struct FinishArgs {
   const int* state_slots;
 };
 
-// RB rows a block: the side input's weights are read once for all of them (a row's sums do not depend on RB).
+// RB rows a block (one, as launched: steps of many rows take the side input as matrix products instead).
 template <typename T, int RB>
 __global__ void __launch_bounds__(256) parallel_finish_kernel(FinishArgs a) {
   pdl_sync();
@@ -313,6 +424,201 @@ __global__ void __launch_bounds__(256) parallel_finish_kernel(FinishArgs a) {
   }
 }
 
+// parallel_finish for few rows: a row is shared by the kFinishCluster CTAs of a thread-block cluster, so that a decode
+// step of a handful of rows still reads the side input's weights with dozens of CTAs. Every CTA forms the whole summed
+// row (the gate's products need all of it) and owns a slice of the gate's outputs and a slice of the columns: the
+// slices of g are gathered, and the parts of sum(y^2) added in rank order, through distributed shared memory.
+constexpr int kFinishCluster = 8;
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ float peer_shared_float(const float* mine, uint32_t rank) {
+  uint32_t addr;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(mine))), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) parallel_finish_cluster_kernel(FinishArgs a) {
+  pdl_sync();
+  extern __shared__ float smem[];
+  const int D = a.D, S = a.side_dim;
+  constexpr int C = kFinishCluster, V = Vec16<T>::N;
+  float* row = smem;                   // [D]: the summed row; this CTA's columns later hold y
+  float* g = row + D;                  // [S]
+  float* scratch = g + S;              // [33]
+  float* part = scratch + 36;          // this CTA's part of sum(y^2)
+  const int rank = static_cast<int>(cluster_rank());
+  const int t = blockIdx.x / C;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int cols = ((D + C - 1) / C + V - 1) / V * V;          // columns a CTA, whole 16-byte pieces
+  const int d_lo = min(D, rank * cols), d_hi = min(D, d_lo + cols);
+  const int outs = (S + C - 1) / C;
+  const int i_lo = min(S, rank * outs), i_hi = min(S, i_lo + outs);
+  float* xr = a.x + static_cast<long long>(t) * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    const long long idx = static_cast<long long>(t) * D + d;
+    const float v = xr[d] + a.mult * (delta_at<T>(a.a, idx) + delta_at<T>(a.b, idx));
+    row[d] = v;
+    if (d >= d_lo && d < d_hi) xr[d] = v;
+  }
+  __syncthreads();
+  {
+    const T* gate = static_cast<const T*>(a.side_gate);
+    const T* table = static_cast<const T*>(a.side_table) + static_cast<long long>(a.tokens[t]) * S;
+    const bool wide = D % V == 0;
+    for (int i = i_lo + warp; i < i_hi; i += nwarps) {
+      const T* wr = gate + static_cast<long long>(i) * D;
+      float dot = 0.0f;
+      if (wide) {
+        for (int d = lane * V; d < D; d += 32 * V) {
+          Vec16<T> w;
+          w.load(wr + d);
+#pragma unroll
+          for (int e = 0; e < V; ++e) dot = fmaf(w.v[e], row[d + e], dot);
+        }
+      } else {
+        for (int d = lane; d < D; d += 32) dot = fmaf(ld(wr + d), row[d], dot);
+      }
+      dot = warp_sum(dot);
+      if (lane == 0) g[i] = gelu_tanh_side(dot) * ld(table + i);
+    }
+  }
+  cluster_sync_all();                  // every CTA's slice of g is written
+  for (int i = threadIdx.x; i < S; i += blockDim.x) {
+    const int owner = i / outs;
+    if (owner != rank) g[i] = peer_shared_float(g + i, owner);
+  }
+  __syncthreads();
+  float ss = 0.0f;
+  {
+    const T* proj = static_cast<const T*>(a.side_proj);
+    const bool wide = S % V == 0;
+    for (int d = d_lo + threadIdx.x; d < d_hi; d += blockDim.x) {
+      const T* wr = proj + static_cast<long long>(d) * S;
+      float y = 0.0f;
+      if (wide) {
+        for (int i = 0; i < S; i += V) {
+          Vec16<T> w;
+          w.load(wr + i);
+#pragma unroll
+          for (int e = 0; e < V; ++e) y = fmaf(w.v[e], g[i + e], y);
+        }
+      } else {
+        for (int i = 0; i < S; ++i) y = fmaf(ld(wr + i), g[i], y);
+      }
+      ss = fmaf(y, y, ss);
+      row[d] = y;
+    }
+  }
+  ss = block_sum(ss, scratch);
+  if (threadIdx.x == 0) *part = ss;
+  cluster_sync_all();                  // every CTA's part is written (and nobody reads a peer's g any more)
+  float total = 0.0f;
+  for (int r = 0; r < C; ++r) total += r == rank ? ss : peer_shared_float(part, r);
+  const float inv = 1.0f / sqrtf(total / static_cast<float>(D) + a.eps);
+  for (int d = d_lo + threadIdx.x; d < d_hi; d += blockDim.x) xr[d] += a.mult * (row[d] * inv) * a.side_norm[d];
+  if (a.R > 0) {
+    const int s = a.seq_of_row[t];
+    const int pos = a.positions[t], slot = a.state_slots[s];
+    if (slot >= 0 && pos >= a.context_lens[s] - a.R) {
+      const float* src = a.unit + static_cast<long long>(t) * D;
+      float* dst = a.ring + (static_cast<long long>(slot) * a.R + pos % a.R) * D;
+      for (int d = d_lo + threadIdx.x; d < d_hi; d += blockDim.x) dst[d] = src[d];
+    }
+  }
+  cluster_sync_all();                  // a CTA's shared memory stays until every peer has read its part
+}
+
+template <typename T>
+static int launch_finish_cluster(const FinishArgs& a, cudaStream_t s) {
+  const size_t smem = (static_cast<size_t>(a.D) + a.side_dim + 48) * sizeof(float);
+  if (smem > 48 * 1024) cudaFuncSetAttribute(parallel_finish_cluster_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(a.T * kFinishCluster);
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attrs[2];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = kFinishCluster;
+  attrs[0].val.clusterDim.y = 1;
+  attrs[0].val.clusterDim.z = 1;
+  attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attrs[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attrs;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  cudaLaunchKernelEx(&cfg, parallel_finish_cluster_kernel<T>, a);
+  TIE_RETURN_LAUNCH("parallel_finish");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) parallel_sum_kernel(float* __restrict__ x, T* __restrict__ copy, int D, float mult, Delta da, Delta db) {
+  pdl_sync();
+  const long long base = static_cast<long long>(blockIdx.x) * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    const float v = x[base + d] + mult * (delta_at<T>(da, base + d) + delta_at<T>(db, base + d));
+    x[base + d] = v;
+    st(copy + base + d, v);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) side_gate_act_kernel(const float* __restrict__ pre, const T* __restrict__ table,
+                                                            const int* __restrict__ tokens, T* __restrict__ g, int S, long long total) {
+  pdl_sync();
+  const long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (e >= total) return;
+  const long long t = e / S;
+  const int i = static_cast<int>(e - t * S);
+  st(g + e, gelu_tanh_side(pre[e]) * ld(table + static_cast<long long>(tokens[t]) * S + i));
+}
+
+struct SideFinishArgs {
+  float* x;
+  const float* y;
+  int D;
+  float mult, eps;
+  const float* w;
+  const float* unit;
+  float* ring;
+  int R;
+  const int* seq_of_row;
+  const int* positions;
+  const int* context_lens;
+  const int* state_slots;
+};
+
+__global__ void __launch_bounds__(256) side_finish_kernel(SideFinishArgs a) {
+  pdl_sync();
+  __shared__ float scratch[40];
+  const int t = blockIdx.x, D = a.D;
+  const float* yr = a.y + static_cast<long long>(t) * D;
+  float* xr = a.x + static_cast<long long>(t) * D;
+  float ss = 0.0f;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) ss = fmaf(yr[d], yr[d], ss);
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / static_cast<float>(D) + a.eps);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) xr[d] += a.mult * (yr[d] * inv) * a.w[d];
+  if (a.R > 0) {
+    const int s = a.seq_of_row[t];
+    const int pos = a.positions[t], slot = a.state_slots[s];
+    if (slot >= 0 && pos >= a.context_lens[s] - a.R) {
+      const float* src = a.unit + static_cast<long long>(t) * D;
+      float* dst = a.ring + (static_cast<long long>(slot) * a.R + pos % a.R) * D;
+      for (int d = threadIdx.x; d < D; d += blockDim.x) dst[d] = src[d];
+    }
+  }
+}
+
 template <typename T, int RB>
 static int launch_finish(const FinishArgs& a, cudaStream_t s) {
   const size_t smem = (static_cast<size_t>(RB) * (a.D + a.side_dim) + 40) * sizeof(float);
@@ -356,7 +662,7 @@ TIE_API int tie_group_norm_taps(int dtype, float* x, const void* delta, const fl
                                 const int* rows, int n, int dim, int groups, float eps, const float* w_a, const float* w_b,
                                 const float* taps_a, const float* taps_b, int taps, void* out_a, void* out_b, float* unit,
                                 const float* ring, const int* seq_of_row, const int* positions, const int* query_start,
-                                const int* context_lens, const int* state_slots, cudaStream_t s) {
+                                const int* context_lens, const int* state_slots, int tile_rows, cudaStream_t s) {
   TIE_REQUIRE(n >= 0 && dim > 0 && groups > 0 && dim % groups == 0, "group_norm_taps: %d columns do not split into %d equal groups",
               dim, groups);
   TIE_REQUIRE(taps >= 0 && taps <= kMaxTaps, "group_norm_taps: at most %d taps, got %d", kMaxTaps, taps);
@@ -378,6 +684,28 @@ TIE_API int tie_group_norm_taps(int dtype, float* x, const void* delta, const fl
   a.out_a = out_a, a.out_b = out_b, a.unit = unit, a.ring = ring;
   a.seq_of_row = seq_of_row, a.positions = positions, a.query_start = query_start, a.context_lens = context_lens;
   a.state_slots = state_slots;
+  if (taps > 0) {
+    // tiles of 2 rows once that still gives every SM several blocks (larger tiles leave too few blocks in flight to hide
+    // the loads); 4 columns a thread where the groups allow
+    const int tile = tile_rows > 0 ? tile_rows : n >= 2 * 4 * 148 ? 2 : 1;
+    TIE_REQUIRE(tile <= 64, "group_norm_taps: tiles of at most 64 rows, got %d", tile);
+    const bool wide = dim % 4 == 0 && (dim / groups) % 4 == 0;
+    const size_t tile_smem = (static_cast<size_t>(tile + taps - 1) * groups + 4 * tile) * sizeof(float);
+    TIE_REQUIRE(tile_smem <= 48 * 1024, "group_norm_taps: %d groups are too many", groups);
+#define TIE_TAPS_CASE(TYPE, W) TIE_LAUNCH((group_norm_taps_tile_kernel<TYPE, W>), ceil_div(n, tile), 256, tile_smem, s, a, tile)
+    if (dtype == TIE_F32) {
+      if (wide) TIE_TAPS_CASE(float, 4);
+      else TIE_TAPS_CASE(float, 1);
+    } else if (dtype == TIE_BF16) {
+      if (wide) TIE_TAPS_CASE(__nv_bfloat16, 4);
+      else TIE_TAPS_CASE(__nv_bfloat16, 1);
+    } else {
+      set_error("group_norm_taps: unknown dtype code %d", dtype);
+      return kBadArgument;
+    }
+#undef TIE_TAPS_CASE
+    TIE_RETURN_LAUNCH("group_norm_taps");
+  }
   const bool summed = taps == 0 && (delta != nullptr || part != nullptr);
   const size_t smem = (static_cast<size_t>(taps > 0 ? taps : 1) * groups + (summed ? dim : 0)) * sizeof(float);
   TIE_REQUIRE(smem <= 200 * 1024, "group_norm_taps: a row of %d columns does not fit shared memory", dim);
@@ -416,13 +744,65 @@ TIE_API int tie_parallel_finish(int dtype, float* x, int rows, int dim, float mu
   a.side_dim = side_dim, a.eps = eps;
   a.unit = unit, a.ring = ring, a.R = ring_rows;
   a.seq_of_row = seq_of_row, a.positions = positions, a.context_lens = context_lens, a.state_slots = state_slots;
-  // four rows a block once that still fills the SMs twice over (and fits shared memory): the side input's weights are then
-  // read once for the four
-  const size_t one = (static_cast<size_t>(dim) + side_dim + 40) * sizeof(float), four = (4 * (static_cast<size_t>(dim) + side_dim) + 40) * sizeof(float);
+  const size_t one = (static_cast<size_t>(dim) + side_dim + 40) * sizeof(float);
   TIE_REQUIRE(one <= 200 * 1024, "parallel_finish: a row of %d columns does not fit shared memory", dim);
-  const bool batch = side_dim > 0 && rows >= 4 * 2 * 148 && four <= 100 * 1024;
-  if (dtype == TIE_F32) return batch ? launch_finish<float, 4>(a, s) : launch_finish<float, 1>(a, s);
-  if (dtype == TIE_BF16) return batch ? launch_finish<__nv_bfloat16, 4>(a, s) : launch_finish<__nv_bfloat16, 1>(a, s);
+  // few rows with a side input: a cluster a row, while all clusters of the launch fit the GPU at once twice over
+  const bool cluster = side_dim > 0 && rows * kFinishCluster <= 2 * 148 && one <= 100 * 1024;
+  if (dtype == TIE_F32) return cluster ? launch_finish_cluster<float>(a, s) : launch_finish<float, 1>(a, s);
+  if (dtype == TIE_BF16) return cluster ? launch_finish_cluster<__nv_bfloat16>(a, s) : launch_finish<__nv_bfloat16, 1>(a, s);
   set_error("parallel_finish: unknown dtype code %d", dtype);
   return kBadArgument;
+}
+
+// x += mult * (delta_a + delta_b) and copy = x in the storage type.
+TIE_API int tie_parallel_sum(int dtype, float* x, void* copy, int rows, int dim, float mult, const void* delta_a, const float* part_a,
+                             long long stride_a, int splits_a, const void* delta_b, const float* part_b, long long stride_b,
+                             int splits_b, cudaStream_t s) {
+  TIE_REQUIRE(rows >= 0 && dim > 0 && x != nullptr && copy != nullptr, "parallel_sum: bad arguments rows=%d dim=%d", rows, dim);
+  TIE_REQUIRE((delta_a == nullptr || part_a == nullptr) && (delta_b == nullptr || part_b == nullptr),
+              "parallel_sum: give a delta or partial sums, not both");
+  if (rows == 0) return kOk;
+  const Delta da{delta_a, part_a, stride_a, splits_a}, db{delta_b, part_b, stride_b, splits_b};
+  if (dtype == TIE_F32) {
+    TIE_LAUNCH((parallel_sum_kernel<float>), rows, 256, 0, s, x, static_cast<float*>(copy), dim, mult, da, db);
+  } else if (dtype == TIE_BF16) {
+    TIE_LAUNCH((parallel_sum_kernel<__nv_bfloat16>), rows, 256, 0, s, x, static_cast<__nv_bfloat16*>(copy), dim, mult, da, db);
+  } else {
+    set_error("parallel_sum: unknown dtype code %d", dtype);
+    return kBadArgument;
+  }
+  TIE_RETURN_LAUNCH("parallel_sum");
+}
+
+// g[t, i] = gelu_tanh(pre[t, i]) * table[tokens[t], i]; pre float [rows, side_dim], g and table in the storage type.
+TIE_API int tie_side_gate_act(int dtype, const float* pre, const void* table, const int* tokens, void* g, int rows, int side_dim,
+                              cudaStream_t s) {
+  TIE_REQUIRE(rows >= 0 && side_dim > 0 && pre != nullptr && table != nullptr && tokens != nullptr && g != nullptr,
+              "side_gate_act: bad arguments rows=%d side_dim=%d", rows, side_dim);
+  const long long total = static_cast<long long>(rows) * side_dim;
+  if (total == 0) return kOk;
+  if (dtype == TIE_F32) {
+    TIE_LAUNCH((side_gate_act_kernel<float>), ceil_div(total, 256), 256, 0, s, pre, static_cast<const float*>(table), tokens,
+               static_cast<float*>(g), side_dim, total);
+  } else if (dtype == TIE_BF16) {
+    TIE_LAUNCH((side_gate_act_kernel<__nv_bfloat16>), ceil_div(total, 256), 256, 0, s, pre, static_cast<const __nv_bfloat16*>(table),
+               tokens, static_cast<__nv_bfloat16*>(g), side_dim, total);
+  } else {
+    set_error("side_gate_act: unknown dtype code %d", dtype);
+    return kBadArgument;
+  }
+  TIE_RETURN_LAUNCH("side_gate_act");
+}
+
+// x += mult * y / rms(y) * w (all float), then the rows of `unit` that are a request's last ring_rows go to its ring.
+TIE_API int tie_side_finish(float* x, const float* y, int rows, int dim, float mult, float eps, const float* w, const float* unit,
+                            float* ring, int ring_rows, const int* seq_of_row, const int* positions, const int* context_lens,
+                            const int* state_slots, cudaStream_t s) {
+  TIE_REQUIRE(rows >= 0 && dim > 0 && x != nullptr && y != nullptr && w != nullptr && ring_rows >= 0, "side_finish: bad arguments rows=%d dim=%d", rows, dim);
+  TIE_REQUIRE(ring_rows == 0 || (unit != nullptr && ring != nullptr && seq_of_row != nullptr && positions != nullptr &&
+                                 context_lens != nullptr && state_slots != nullptr), "side_finish: the ring needs the step's index arrays");
+  if (rows == 0) return kOk;
+  SideFinishArgs a{x, y, dim, mult, eps, w, unit, ring, ring_rows, seq_of_row, positions, context_lens, state_slots};
+  TIE_LAUNCH(side_finish_kernel, rows, 256, 0, s, a);
+  TIE_RETURN_LAUNCH("side_finish");
 }

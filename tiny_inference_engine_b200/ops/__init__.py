@@ -1126,12 +1126,13 @@ def add_row_vector(x, vec) -> None:
 
 
 def group_norm_taps(x, groups: int, eps: float, w_a, out_a, w_b=None, out_b=None, taps_a=None, taps_b=None, ctx=None, unit=None,
-                    ring=None, delta=None, rows=None) -> None:
+                    ring=None, delta=None, rows=None, tile: int = 0) -> None:
     """u = x / rms over each of `groups` equal parts of a row; out_a = w_a * (u_t + sum_j taps_a[:, j] u_(t - taps + 1 + j)) and
     likewise out_b (optional): a grouped RMS norm whose output passes h + conv(h), a causal convolution over time per channel.
     With taps, `ctx` gives the step's index arrays, `ring` [slots, taps - 1, D] float32 the unit rows of earlier steps (by
     position mod taps - 1) and `unit` [T, D] receives the rows that `parallel_finish` moves into the ring. Without taps it is the
-    grouped norm alone: `delta` (tensor or SplitSum) is added to x first and `rows` gathers (x is then left as it is)."""
+    grouped norm alone: `delta` (tensor or SplitSum) is added to x first and `rows` gathers (x is then left as it is). `tile`:
+    rows a block with taps (0: chosen by the number of rows; the result does not depend on it)."""
     T, D = x.shape
     taps = 0 if taps_a is None else taps_a.shape[1]
     _dev(x, w_a, w_b, out_a, out_b, taps_a, taps_b, unit, ring, rows)
@@ -1160,7 +1161,7 @@ def group_norm_taps(x, groups: int, eps: float, w_a, out_a, w_b=None, out_b=None
     idx = (ctx.seq_of_row, ctx.positions, ctx.query_start, ctx.context_lens, ctx.state_slots) if taps > 0 else (None,) * 5
     call("tie_group_norm_taps", dtype_code(out_a), x.data_ptr(), dp, pp, ps, sp, _ptr(rows), n, D, int(groups), float(eps),
          w_a.data_ptr(), _ptr(w_b), _ptr(taps_a), _ptr(taps_b), taps, out_a.data_ptr(), _ptr(out_b), _ptr(unit), _ptr(ring),
-         *(_ptr(t) for t in idx), _stream())
+         *(_ptr(t) for t in idx), int(tile), _stream())
 
 
 def parallel_finish(x, mult: float, delta_a, delta_b, dtype, ctx=None, side=None, eps: float = 0.0, unit=None, ring=None) -> None:
@@ -1192,6 +1193,42 @@ def parallel_finish(x, mult: float, delta_a, delta_b, dtype, ctx=None, side=None
          ctx.tokens.data_ptr() if need_ctx else 0, _ptr(table), _ptr(gate), _ptr(proj), _ptr(norm), n, float(eps), _ptr(unit) if R else 0,
          _ptr(ring) if R else 0, R, *((ctx.seq_of_row.data_ptr(), ctx.positions.data_ptr(), ctx.context_lens.data_ptr(),
                                       ctx.state_slots.data_ptr()) if need_ctx else (0, 0, 0, 0)), _stream())
+
+
+def parallel_sum(x, mult: float, delta_a, delta_b, copy) -> None:
+    """x += mult * (delta_a + delta_b) in float32 (each a tensor of copy's dtype, a SplitSum or None); copy = x in its own dtype."""
+    _dev(x, copy)
+    _need(x.dtype == torch.float32 and x.is_contiguous() and copy.shape == x.shape and copy.is_contiguous(),
+          "parallel_sum: x float32 contiguous, copy of the same shape")
+    for d in (delta_a, delta_b):
+        _need(d is None or isinstance(d, SplitSum) or d.dtype == copy.dtype, "parallel_sum: a delta tensor must be of the compute dtype")
+    a, b = _delta_args(delta_a, x, "parallel_sum"), _delta_args(delta_b, x, "parallel_sum")
+    call("tie_parallel_sum", dtype_code(copy), x.data_ptr(), copy.data_ptr(), x.shape[0], x.shape[1], float(mult), *a, *b, _stream())
+
+
+def side_gate_act(pre, table, tokens, g) -> None:
+    """g[t] = gelu_tanh(pre[t]) * table[tokens[t]]: pre float32 [T, n], table [vocab, n] and g [T, n] of one dtype."""
+    _dev(pre, table, tokens, g)
+    T, n = pre.shape
+    _need(pre.dtype == torch.float32 and pre.is_contiguous() and g.shape == (T, n) and g.is_contiguous() and table.dim() == 2 and
+          table.shape[1] == n and table.is_contiguous() and table.dtype == g.dtype and tokens.dtype == torch.int32 and
+          tokens.numel() >= T, "side_gate_act: pre float32 [T, n], table [vocab, n], g [T, n], tokens int32 [T]")
+    call("tie_side_gate_act", dtype_code(g), pre.data_ptr(), table.data_ptr(), tokens.data_ptr(), g.data_ptr(), T, n, _stream())
+
+
+def side_finish(x, y, mult: float, eps: float, norm, ctx=None, unit=None, ring=None) -> None:
+    """x += mult * y / rms(y) * norm, all float32; with `ring`, the ring update of `parallel_finish`."""
+    _dev(x, y, norm, unit, ring)
+    T, D = x.shape
+    _need(x.dtype == torch.float32 and x.is_contiguous() and y.dtype == torch.float32 and y.shape == x.shape and y.is_contiguous() and
+          norm.dtype == torch.float32 and norm.numel() == D, "side_finish: x, y float32 [T, D], norm float32 [D]")
+    R = 0 if ring is None else ring.shape[1]
+    if R:
+        _need(ring.dtype == torch.float32 and ring.is_contiguous() and ring.shape[2] == D and unit is not None and
+              unit.dtype == torch.float32 and unit.shape == (T, D) and unit.is_contiguous(), "side_finish: ring float32 [slots, R, D], unit float32 [T, D]")
+    call("tie_side_finish", x.data_ptr(), y.data_ptr(), T, D, float(mult), float(eps), norm.data_ptr(), _ptr(unit) if R else 0,
+         _ptr(ring) if R else 0, R, *((ctx.seq_of_row.data_ptr(), ctx.positions.data_ptr(), ctx.context_lens.data_ptr(),
+                                      ctx.state_slots.data_ptr()) if R else (0, 0, 0, 0)), _stream())
 
 
 # -- attention whose scores are mixed across heads, with a sink (csrc/attention_mixed.cu)

@@ -71,8 +71,11 @@ _SIGNATURES = {
     "tie_gemm_tc_grouped": [I, P, P, P, I, I, I, L, L, I, I, P, P, P],
     "tie_pair_hash_add": [I, P, P, P, P, P, P, P, P, I, L, L, I, I, P],
     "tie_add_row_vector": [P, P, I, I, P],
-    "tie_group_norm_taps": [I, P, P, P, L, I, P, I, I, I, F, P, P, P, P, I, P, P, P, P, P, P, P, P, P, P],
+    "tie_group_norm_taps": [I, P, P, P, L, I, P, I, I, I, F, P, P, P, P, I, P, P, P, P, P, P, P, P, P, I, P],
     "tie_parallel_finish": [I, P, I, I, F, P, P, L, I, P, P, L, I, P, P, P, P, P, I, F, P, P, I, P, P, P, P, P],
+    "tie_parallel_sum": [I, P, P, I, I, F, P, P, L, I, P, P, L, I, P],
+    "tie_side_gate_act": [I, P, P, P, P, I, I, P],
+    "tie_side_finish": [P, P, I, I, F, F, P, P, P, I, P, P, P, P, P],
     "tie_rope_pairs_unit_append": [I, P, L, I, I, I, P, I, I, F, P, P, P, P, I, I, I, I, I, I, P],
     "tie_attention_mixed_tc": [P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P, I, I, P, P],
     "tie_attention_mixed": [I, P, L, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P, I, I, I, P, P],

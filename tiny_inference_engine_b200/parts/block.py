@@ -102,6 +102,9 @@ class SandwichNormBlock(Block):
         return self._normed(self.ffn.forward(h, ctx), self.ffn_post_norm)
 
 
+SIDE_PRODUCT_ROWS = 256      # from this many rows of a step on, a parallel block's token side input runs as two matrix products
+
+
 class ParallelBlock(Block):
     """Both sublayers read the same stream, side by side, and join it with one factor:
 
@@ -118,6 +121,10 @@ class ParallelBlock(Block):
     Then, optionally (`side`), a token input of the layer: e = table[token] (a slice of `side.table`, `side.dim` wide,
     at column `side.index * side.dim`), g = gelu_tanh(W_gate x) * e, y = W_proj g,
     x += mult * y / sqrt(mean(y^2) + eps) * w_norm, on the stream as the sublayers left it.
+
+    Few rows (decoding) take the side input in the kernel that also adds the sublayers' outputs; from `SIDE_PRODUCT_ROWS` rows on
+    its two products are matrix products (the stream's copy in the compute dtype times W_gate, g times W_proj into float32)
+    between three small kernels.
 
     A layer may have no feed-forward. The stream, its sums, the norms and the convolution are float32. The block leaves
     the stream complete (it hands on no pending delta). params: `residual_mult`, `taps`, `conv_names`, `side`
@@ -191,6 +198,10 @@ class ParallelBlock(Block):
             self.side = (table, to_compute(get(self.prefix + s["gate"]), self.dtype).contiguous(),
                          to_compute(get(self.prefix + s["proj"]), self.dtype).contiguous(), f32(self.prefix + s["norm"]))
             self.side_eps = float(s.get("eps", self.eps))
+            from .. import ops
+            # the same two weights for the many-row path (a second copy: a few hundred KB a layer)
+            self.gemm_gate = ops.bound_gemm(self.side[1].clone(), split_many=False)
+            self.gemm_proj = ops.bound_gemm(self.side[2].clone(), split_many=False)
 
     def state_need(self):
         from .base import StateNeed
@@ -215,6 +226,18 @@ class ParallelBlock(Block):
                             self.taps_a, self.taps_b, ctx=ctx, unit=unit, ring=ring)
         mixed = self.mixer.forward(h1, ctx, cache, None)
         fed = self.ffn.forward(h2, ctx) if self.has_ffn else None
+        if self.side is not None and T >= SIDE_PRODUCT_ROWS:
+            n = self.side[1].shape[0]
+            copy = ctx.ws.rows("pblock.copy", T, D, self.dtype)
+            ops.parallel_sum(x, self.mult, mixed, fed, copy)
+            pre = ctx.ws.rows("pblock.side.pre", T, n, torch.float32)
+            self.gemm_gate(copy, pre)
+            g = ctx.ws.rows("pblock.side.g", T, n, self.dtype)
+            ops.side_gate_act(pre, self.side[0], ctx.tokens, g)
+            y = ctx.ws.rows("pblock.side.y", T, D, torch.float32)
+            self.gemm_proj(g, y)
+            ops.side_finish(x, y, self.mult, self.side_eps, self.side[3], ctx=ctx, unit=unit, ring=ring)
+            return None
         ops.parallel_finish(x, self.mult, mixed, fed, self.dtype, ctx=ctx, side=self.side,
                             eps=self.side_eps if self.side is not None else 0.0, unit=unit, ring=ring)
         return None
