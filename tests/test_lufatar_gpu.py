@@ -387,6 +387,56 @@ def test_the_token_side_input_as_matrix_products(tmp_path, truth, name, dtype, m
     close(hs.in_portions("p", toks, [40, 3, 12, 1, 30, 11, 2]), want, dtype, f"{name} in portions")
 
 
+@pytest.mark.parametrize("shape", [(256, 16, 3), (36, 5, 1), (2048, 64, 2), (40, 8, 0)])
+def test_sublayer_sum_and_token_side_input_for_few_and_for_more_rows(shape):
+    """x += mult * (a + b), the token side input and the ring update: a handful of rows (a thread-block cluster a row,
+    many times over: the CTAs of a cluster read the row that one of them writes), some dozens of rows (a block a row)
+    and the three kernels around two matrix products, against the plain rule."""
+    from types import SimpleNamespace
+    from tiny_inference_engine_b200 import ops
+    D, S, R = shape
+    rng = np.random.default_rng(D + S)
+    vocab, mult, eps = 50, 0.7, 1e-5
+    table, gate = rng.standard_normal((vocab, S)).astype(np.float32), (rng.standard_normal((S, D)) / np.sqrt(D)).astype(np.float32)
+    proj, norm = rng.standard_normal((D, S)).astype(np.float32), rng.standard_normal(D).astype(np.float32)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device="cuda")
+    side = tuple(dev(a) for a in (table, gate, proj, norm))
+    for T in (5, 40):
+        x, da, db = (rng.standard_normal((T, D)).astype(np.float32) for _ in range(3))
+        tokens = rng.integers(0, vocab, T)
+        unit = rng.standard_normal((T, D)).astype(np.float32)
+        ring0 = rng.standard_normal((2, max(R, 1), D)).astype(np.float32)
+        first = 7                                           # one sequence, rows at positions 7 .. 7 + T - 1, slot 1
+        xs = x.astype(np.float64) + mult * (da.astype(np.float64) + db)
+        g = plain.gelu_tanh(xs @ gate.T.astype(np.float64)) * table[tokens]
+        y = g @ proj.T.astype(np.float64)
+        want = xs + mult * y / np.sqrt((y * y).mean(-1, keepdims=True) + eps) * norm
+        want_ring = ring0.copy()
+        for i in range(max(0, T - R), T):
+            want_ring[1, (first + i) % R] = unit[i]
+        ctx = SimpleNamespace(tokens=i32(tokens), seq_of_row=i32([0] * T), positions=i32(range(first, first + T)),
+                              context_lens=i32([first + T]), state_slots=i32([1]))
+        for _ in range(25 if T == 5 else 2):
+            xd, ring = dev(x), dev(ring0)
+            ops.parallel_finish(xd, mult, dev(da), dev(db), torch.float32, ctx=ctx, side=side, eps=eps, unit=dev(unit) if R else None,
+                                ring=ring if R else None)
+            assert np.abs(xd.cpu().numpy() - want).max() <= 2e-5 * np.abs(want).max(), f"{T} rows"
+            if R:
+                assert np.array_equal(ring.cpu().numpy(), want_ring), f"the ring after {T} rows"
+        # the same through the kernels of the many-row path
+        xd, ring, copy = dev(x), dev(ring0), torch.zeros((T, D), dtype=torch.float32, device="cuda")
+        ops.parallel_sum(xd, mult, dev(da), dev(db), copy)
+        assert np.abs(copy.cpu().numpy() - xs).max() <= 1e-5 * np.abs(xs).max() and torch.equal(copy, xd)
+        gd = torch.zeros((T, S), dtype=torch.float32, device="cuda")
+        ops.side_gate_act(dev((xs @ gate.T.astype(np.float64)).astype(np.float32)), side[0], ctx.tokens, gd)
+        assert np.abs(gd.cpu().numpy() - g).max() <= 1e-5 * np.abs(g).max()
+        ops.side_finish(xd, dev(y.astype(np.float32)), mult, eps, side[3], ctx=ctx, unit=dev(unit) if R else None, ring=ring if R else None)
+        assert np.abs(xd.cpu().numpy() - want).max() <= 2e-5 * np.abs(want).max()
+        if R:
+            assert np.array_equal(ring.cpu().numpy(), want_ring)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("shape", [(32, 2, 4), (36, 3, 2), (64, 1, 3), (24, 4, 1)])
 def test_grouped_norm_with_taps_in_tiles_of_rows(shape, dtype):

@@ -64,6 +64,54 @@ __device__ __forceinline__ void load_plane_tiles(uint32_t dst, const __nv_bfloat
   }
 }
 
+__device__ __forceinline__ void sts_f2(uint32_t addr, float x, float y) {
+  asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(x), "f"(y) : "memory");
+}
+__device__ __forceinline__ float2 lds_f2(uint32_t addr) {
+  float2 v;
+  asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ float lds_f(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
+}
+
+__device__ __forceinline__ void sts_u4(uint32_t addr, const uint32_t (&v)[4]) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]) : "memory");
+}
+__device__ __forceinline__ void lds_u4(uint32_t (&v)[4], uint32_t addr) {
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(addr));
+}
+
+// Q K^T of a warp's 16 rows against a K tile, like qk_tile, with the Q fragments of the first KREG k-steps in registers
+// and the others in shared memory as the lanes left them (16 bytes a lane and k-step at `kept`).
+template <int DK, int NT, int KREG>
+__device__ __forceinline__ void qk_rows(float (&s)[NT][4], const uint32_t (&qf)[KREG][4], uint32_t kept, uint32_t k_tile) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int ks = 0; ks < DK / 16; ++ks) {
+    uint32_t a[4];
+    if (ks < KREG) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) a[e] = qf[ks < KREG ? ks : 0][e];
+    } else {
+      lds_u4(a, kept + (ks - KREG) * 512);
+    }
+#pragma unroll
+    for (int np = 0; np < NT / 2; ++np) {
+      uint32_t b[4];
+      const int r = np * 16 + (lane & 7) + ((lane >> 4) << 3);
+      const int c = ks * 2 + ((lane >> 3) & 1);
+      ldmatrix_x4(b, k_tile + swz<DK>(r, c));
+      mma_bf16(s[2 * np], a, b[0], b[1]);
+      mma_bf16(s[2 * np + 1], a, b[2], b[3]);
+    }
+  }
+}
+
+// MAXT 512: blocks of more than 256 threads have 128 registers a thread; half of the Q fragments then stay in shared memory.
 template <int DK, int DV, int NT, int MAXT>
 __global__ void __launch_bounds__(MAXT, 1) attn_mixed_tc_kernel(MixedTcArgs a) {
   pdl_sync();
@@ -103,6 +151,8 @@ __global__ void __launch_bounds__(MAXT, 1) attn_mixed_tc_kernel(MixedTcArgs a) {
   float* raw = reinterpret_cast<float*>(smem + k_bytes + second);              // [H][MQ][RS]
   float* mixs = raw + H * MQ * RS;                                              // [H][H], times scale * log2 e
   int* rows = reinterpret_cast<int*>(mixs + H * H);                             // [2][KT]
+  constexpr int KREG = MAXT > 256 ? DK / 32 : DK / 16;                          // k-steps whose Q fragments stay in registers
+  const uint32_t kept = ((smem_addr(rows + 2 * KT) + 15u) & ~15u) + (warp * (DK / 16 - KREG) * 32 + lane) * 16;   // [warps][DK / 16 - KREG][32] x 16 bytes
 
   const int tile0 = lo / KT;
   const int n_tiles = hi_cta / KT - tile0 + 1;
@@ -127,24 +177,38 @@ __global__ void __launch_bounds__(MAXT, 1) attn_mixed_tc_kernel(MixedTcArgs a) {
   cp_async_commit();
   cp_async_wait<1>();            // Q has landed
   __syncthreads();
-  uint32_t qf[DK / 16][4];
+  uint32_t qf[KREG][4];
 #pragma unroll
-  for (int ks = 0; ks < DK / 16; ++ks) ldmatrix_x4(qf[ks], v_buf + swz<DK>(warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
+  for (int ks = 0; ks < DK / 16; ++ks) {
+    if (ks < KREG) {
+      ldmatrix_x4(qf[ks < KREG ? ks : 0], v_buf + swz<DK>(warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
+    } else {
+      uint32_t f[4];
+      ldmatrix_x4(f, v_buf + swz<DK>(warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
+      sts_u4(kept + (ks - KREG) * 512, f);       // read back by the same lane only
+    }
+  }
   __syncthreads();               // the Q tile's room becomes the V buffer
   load_plane_tiles<DV, KT>(v_buf, a.v_cache, rows + (tile0 & 1) * KT, G, a.page_size);
   cp_async_commit();
 
   const int gq = lane >> 2, tq = lane & 3;
-  int row_lim[2], row_head[2], row_q[2];
-  int warp_hi = -1;
+  // this thread's two rows (gq and gq + 8 of the warp's 16): head hb + r / qpw, query position sub * qpw + r % qpw
+  int row_lim[2];
+  uint32_t my_raw[2], mix_row[2], src[2];       // shared-memory addresses: where the row's raw scores go, its row of the mix,
+                                                // and head 0's raw scores of its query position
+  const uint32_t raw_addr = smem_addr(raw), mix_addr = smem_addr(mixs);
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     const int r = gq + 8 * half;
-    row_head[half] = hb + r / qpw;
-    row_q[half] = sub * qpw + r % qpw;
-    const int qi = q0 + row_q[half];
+    const int head = hb + r / qpw, ql = sub * qpw + r % qpw;
+    const int qi = q0 + ql;
     row_lim[half] = qi < nq ? min(pos0 + qi, hi_cta) : -1;
+    my_raw[half] = raw_addr + ((head * MQ + ql) * RS + tq * 2) * 4;
+    mix_row[half] = mix_addr + head * H * 4;
+    src[half] = raw_addr + (ql * RS + tq * 2) * 4;
   }
+  int warp_hi = -1;
   {
     const int q_last = min(nq - 1, q0 + sub * qpw + qpw - 1);
     if (q0 + sub * qpw < nq) warp_hi = min(pos0 + q_last, hi_cta);
@@ -156,13 +220,7 @@ __global__ void __launch_bounds__(MAXT, 1) attn_mixed_tc_kernel(MixedTcArgs a) {
   float acc[DV / 8][4];
 #pragma unroll
   for (int j = 0; j < DV / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
-  float* my_raw0 = raw + (static_cast<long long>(row_head[0]) * MQ + row_q[0]) * RS + tq * 2;
-  float* my_raw1 = raw + (static_cast<long long>(row_head[1]) * MQ + row_q[1]) * RS + tq * 2;
-  const float* mix_row0 = mixs + row_head[0] * H;
-  const float* mix_row1 = mixs + row_head[1] * H;
-  const float* src0 = raw + static_cast<long long>(row_q[0]) * RS + tq * 2;      // head g: + g * MQ * RS
-  const float* src1 = raw + static_cast<long long>(row_q[1]) * RS + tq * 2;
-  const int head_stride = MQ * RS;
+  const uint32_t head_stride = MQ * RS * 4;
 
   for (int i = 0; i < n_tiles; ++i) {
     const int tile = tile0 + i;
@@ -175,11 +233,11 @@ __global__ void __launch_bounds__(MAXT, 1) attn_mixed_tc_kernel(MixedTcArgs a) {
     if (active) {
 #pragma unroll
       for (int j = 0; j < NT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
-      qk_tile<DK, NT>(s, qf, k_buf + kvh * (KT * DK * 2), 0);
+      qk_rows<DK, NT, KREG>(s, qf, kept, k_buf + kvh * (KT * DK * 2));
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
-        *reinterpret_cast<float2*>(my_raw0 + j * 8) = make_float2(s[j][0], s[j][1]);
-        *reinterpret_cast<float2*>(my_raw1 + j * 8) = make_float2(s[j][2], s[j][3]);
+        sts_f2(my_raw[0] + j * 32, s[j][0], s[j][1]);
+        sts_f2(my_raw[1] + j * 32, s[j][2], s[j][3]);
       }
     }
     cp_async_wait<0>();          // this tile's V
@@ -190,13 +248,12 @@ __global__ void __launch_bounds__(MAXT, 1) attn_mixed_tc_kernel(MixedTcArgs a) {
 #pragma unroll
       for (int j = 0; j < NT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
       for (int g = 0; g < H; ++g) {
-        const float w0 = mix_row0[g], w1 = mix_row1[g];
-        const float* p0 = src0 + g * head_stride;
-        const float* p1 = src1 + g * head_stride;
+        const float w0 = lds_f(mix_row[0] + g * 4), w1 = lds_f(mix_row[1] + g * 4);
+        const uint32_t p0 = src[0] + g * head_stride, p1 = src[1] + g * head_stride;
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
-          const float2 lo2 = *reinterpret_cast<const float2*>(p0 + j * 8);
-          const float2 hi2 = *reinterpret_cast<const float2*>(p1 + j * 8);
+          const float2 lo2 = lds_f2(p0 + j * 32);
+          const float2 hi2 = lds_f2(p1 + j * 32);
           s[j][0] = fmaf(w0, lo2.x, s[j][0]);
           s[j][1] = fmaf(w0, lo2.y, s[j][1]);
           s[j][2] = fmaf(w1, hi2.x, s[j][2]);
@@ -223,9 +280,10 @@ __global__ void __launch_bounds__(MAXT, 1) attn_mixed_tc_kernel(MixedTcArgs a) {
   const int DVs = DV + 2;
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
-    const int qi = q0 + row_q[half];
+    const int r = gq + 8 * half;
+    const int qi = q0 + sub * qpw + r % qpw;
     if (qi >= nq) continue;
-    const int h = row_head[half];
+    const int h = hb + r / qpw;
     if (split_mode) {
       // the sums as they are, the maximum in natural units, the weight sum: attention_merge joins the splits
       float* dst = a.scratch + ((static_cast<long long>(li) * H + h) * a.max_splits + split) * DVs;
@@ -253,12 +311,14 @@ struct MixedTcPlan {
 
 static int gcd_int(int a, int b) { return b == 0 ? a : gcd_int(b, a % b); }
 
-// Shared memory of a block: K tiles, V tiles (or the Q tile if larger), raw scores, the mix, key rows of two tiles.
+// Shared memory of a block: K tiles, V tiles (or the Q tile if larger), raw scores, the mix, key rows of two tiles, and
+// for blocks of more than 8 warps half of the Q fragments.
 static size_t mixed_tc_smem(int heads, int kv_heads, int dim, int vdim, int warps, int mq, int kt) {
   const size_t k = static_cast<size_t>(kv_heads) * kt * dim * 2, v = static_cast<size_t>(kv_heads) * kt * vdim * 2;
   const size_t q = static_cast<size_t>(warps) * 16 * dim * 2;
   const size_t second = ((v > q ? v : q) + 127) / 128 * 128;
-  return k + second + static_cast<size_t>(heads) * mq * (kt + 8) * 4 + static_cast<size_t>(heads) * heads * 4 + 2 * kt * 4;
+  const size_t kept = warps > 8 ? static_cast<size_t>(warps) * (dim / 32) * 512 + 16 : 0;      // Q fragments that leave the registers, on 16 bytes
+  return k + second + static_cast<size_t>(heads) * mq * (kt + 8) * 4 + static_cast<size_t>(heads) * heads * 4 + 2 * kt * 4 + kept;
 }
 
 constexpr size_t kMixedTcSmemLimit = 208 * 1024;

@@ -467,8 +467,7 @@ __global__ void __launch_bounds__(256) parallel_finish_cluster_kernel(FinishArgs
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     const long long idx = static_cast<long long>(t) * D + d;
     const float v = xr[d] + a.mult * (delta_at<T>(a.a, idx) + delta_at<T>(a.b, idx));
-    row[d] = v;
-    if (d >= d_lo && d < d_hi) xr[d] = v;
+    row[d] = v;               // x itself is written after the cluster's first barrier: until then the peers read it
   }
   __syncthreads();
   {
@@ -492,7 +491,8 @@ __global__ void __launch_bounds__(256) parallel_finish_cluster_kernel(FinishArgs
       if (lane == 0) g[i] = gelu_tanh_side(dot) * ld(table + i);
     }
   }
-  cluster_sync_all();                  // every CTA's slice of g is written
+  cluster_sync_all();                  // every CTA's slice of g is written, and every CTA has read the row of x
+  for (int d = d_lo + threadIdx.x; d < d_hi; d += blockDim.x) xr[d] = row[d];
   for (int i = threadIdx.x; i < S; i += blockDim.x) {
     const int owner = i / outs;
     if (owner != rank) g[i] = peer_shared_float(g + i, owner);
