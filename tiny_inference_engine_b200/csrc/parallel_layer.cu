@@ -190,7 +190,7 @@ template <int W> __device__ __forceinline__ void load_vec(const float* p, float 
 // before it are computed once (a warp per row and group), then every row of the tile forms its outputs, W columns a
 // thread at a time. A row's numbers do not depend on the tile it falls into.
 template <typename T, int W>
-__global__ void __launch_bounds__(256) group_norm_taps_tile_kernel(NormTapsArgs a, int tile) {
+__global__ void __launch_bounds__(256, 4) group_norm_taps_tile_kernel(NormTapsArgs a, int tile) {
   pdl_sync();
   extern __shared__ float smem[];
   float* inv = smem;                       // [(tile + R) * groups], row t0 - R first
