@@ -480,7 +480,7 @@ def test_grouped_norm_with_taps_in_tiles_of_rows(shape, dtype):
     for tile in (1, 5, 8):
         oa, ob = torch.zeros((T, D), dtype=dtype, device="cuda"), torch.zeros((T, D), dtype=dtype, device="cuda")
         left = torch.zeros((T, D), dtype=torch.float32, device="cuda")
-        ops.group_norm_taps(dev(x), groups, eps, dev(wa), oa, dev(wb), ob, dev(ta), dev(tb), ctx=ctx, unit=left if R else None,
+        ops.group_norm_taps(dev(x), groups, eps, dev(wa), oa, dev(wb), ob, dev(ta.T), dev(tb.T), ctx=ctx, unit=left if R else None,
                             ring=dev(ring) if R else None, tile=tile)
         outs.append((oa.float().cpu().numpy(), ob.float().cpu().numpy(), left.cpu().numpy()))
     tol = 1e-5 if dtype == torch.float32 else 1e-2

@@ -6,7 +6,8 @@
 //                     portion's last token there (no other block touches the slot).
 //   add_row_vector    x[t] += vec for every row (one learned vector ahead of a pass over a span of layers).
 //   group_norm_taps   u = x / rms over each of `groups` equal parts of the row (float). Outputs, one per sublayer:
-//                     out_a = w_a * (u_t + sum_j taps_a[:, j] * u_(t - taps + 1 + j)), that is h + conv(h) for h = u * w_a,
+//                     out_a = w_a * (u_t + sum_j taps_a[j] * u_(t - taps + 1 + j)) (taps_a [taps, D]: a tap of every
+//                     channel side by side, for coalesced reads), that is h + conv(h) for h = u * w_a,
 //                     a causal convolution over time per channel with zeros ahead of the sequence. Rows of this step
 //                     are renormed from x (x is complete when the kernel starts); rows of earlier steps come from the
 //                     request's state, a ring of the last taps - 1 unit rows indexed by position. The rows that will
@@ -87,7 +88,7 @@ struct NormTapsArgs {
   float eps;
   const float* w_a;
   const float* w_b;         // null: one output
-  const float* taps_a;      // [D, taps] float (null with taps == 0)
+  const float* taps_a;      // [taps, D] float (null with taps == 0)
   const float* taps_b;
   int taps;
   void* out_a;
@@ -101,26 +102,19 @@ struct NormTapsArgs {
   const int* state_slots;
 };
 
+// The grouped norm alone (no taps): optionally a delta added to x first, optionally gathered rows. A block a row.
 template <typename T>
 __global__ void __launch_bounds__(256) group_norm_taps_kernel(NormTapsArgs a) {
   pdl_sync();
   extern __shared__ float smem[];
-  float* inv = smem;                       // [(R + 1) * groups]
+  float* inv = smem;                       // [groups]
   const int i = blockIdx.x;
   const int t = a.rows != nullptr ? a.rows[i] : i;
-  const int D = a.D, R = a.taps > 0 ? a.taps - 1 : 0;
+  const int D = a.D;
   const int gsize = D / a.groups;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  int pos = 0, first = 0, slot = -1, ctx = 0;
-  if (a.taps > 0) {
-    const int s = a.seq_of_row[t];
-    pos = a.positions[t];
-    first = pos - (t - a.query_start[s]);      // position of the portion's first row
-    slot = a.state_slots[s];
-    ctx = a.context_lens[s];
-  }
   float* xr = a.x + static_cast<long long>(t) * D;
-  if (a.taps == 0 && (a.delta.tensor != nullptr || a.delta.part != nullptr)) {
+  if (a.delta.tensor != nullptr || a.delta.part != nullptr) {
     float* row = smem + a.groups;          // the summed row, kept for both passes
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
       const float v = xr[d] + delta_at<T>(a.delta, static_cast<long long>(t) * D + d);
@@ -130,43 +124,18 @@ __global__ void __launch_bounds__(256) group_norm_taps_kernel(NormTapsArgs a) {
     __syncthreads();
     xr = row;
   }
-  for (int item = warp; item < (R + 1) * a.groups; item += nwarps) {
-    const int r = item / a.groups, g = item - r * a.groups;
-    if (r > 0 && pos - r < first) continue;      // a row of an earlier step (or none): no norm to compute
-    const float* src = xr - static_cast<long long>(r) * D + g * gsize;
+  for (int g = warp; g < a.groups; g += nwarps) {
+    const float* src = xr + g * gsize;
     float ss = 0.0f;
     for (int d = lane; d < gsize; d += 32) ss = fmaf(src[d], src[d], ss);
     ss = warp_sum(ss);
-    if (lane == 0) inv[item] = 1.0f / sqrtf(ss / static_cast<float>(gsize) + a.eps);
+    if (lane == 0) inv[g] = 1.0f / sqrtf(ss / static_cast<float>(gsize) + a.eps);
   }
   __syncthreads();
-  const bool keep = a.taps > 1 && pos >= ctx - R;
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    const int g = d / gsize;
-    float u[kMaxTaps];
-    u[0] = xr[d] * inv[g];
-#pragma unroll
-    for (int r = 1; r < kMaxTaps; ++r) {
-      if (r > R) break;
-      const int p = pos - r;
-      float v = 0.0f;
-      if (p >= first) v = xr[d - static_cast<long long>(r) * D] * inv[r * a.groups + g];
-      else if (p >= 0 && slot >= 0) v = a.ring[(static_cast<long long>(slot) * R + p % R) * D + d];
-      u[r] = v;
-    }
-    float sa = u[0], sb = u[0];
-    if (a.taps > 0) {
-#pragma unroll
-      for (int j = 0; j < kMaxTaps; ++j) {
-        if (j >= a.taps) break;
-        const float v = u[a.taps - 1 - j];
-        sa = fmaf(a.taps_a[static_cast<long long>(d) * a.taps + j], v, sa);
-        if (a.w_b != nullptr) sb = fmaf(a.taps_b[static_cast<long long>(d) * a.taps + j], v, sb);
-      }
-    }
-    st(static_cast<T*>(a.out_a) + static_cast<long long>(i) * D + d, a.w_a[d] * sa);
-    if (a.w_b != nullptr) st(static_cast<T*>(a.out_b) + static_cast<long long>(i) * D + d, a.w_b[d] * sb);
-    if (keep) a.unit[static_cast<long long>(t) * D + d] = u[0];
+    const float u = xr[d] * inv[d / gsize];
+    st(static_cast<T*>(a.out_a) + static_cast<long long>(i) * D + d, a.w_a[d] * u);
+    if (a.w_b != nullptr) st(static_cast<T*>(a.out_b) + static_cast<long long>(i) * D + d, a.w_b[d] * u);
   }
 }
 
@@ -190,7 +159,7 @@ template <int W> __device__ __forceinline__ void load_vec(const float* p, float 
 // before it are computed once (a warp per row and group), then every row of the tile forms its outputs, W columns a
 // thread at a time. A row's numbers do not depend on the tile it falls into.
 template <typename T, int W>
-__global__ void __launch_bounds__(256, 4) group_norm_taps_tile_kernel(NormTapsArgs a, int tile) {
+__global__ void __launch_bounds__(256) group_norm_taps_tile_kernel(NormTapsArgs a, int tile) {
   pdl_sync();
   extern __shared__ float smem[];
   float* inv = smem;                       // [(tile + R) * groups], row t0 - R first
@@ -256,19 +225,33 @@ __global__ void __launch_bounds__(256, 4) group_norm_taps_tile_kernel(NormTapsAr
       }
       float oa[W], ob[W];
 #pragma unroll
-      for (int e = 0; e < W; ++e) {
-        float sa = u[0][e], sb = u[0][e];
-        const float* ta = a.taps_a + static_cast<long long>(d + e) * a.taps;
-        const float* tb = a.w_b != nullptr ? a.taps_b + static_cast<long long>(d + e) * a.taps : ta;
+      for (int e = 0; e < W; ++e) oa[e] = ob[e] = u[0][e];
 #pragma unroll
-        for (int r = kMaxTaps - 1; r >= 0; --r) {       // tap taps - 1 - r reads the row r back; the oldest row first
-          if (r <= R) {
-            sa = fmaf(ta[R - r], u[r][e], sa);
-            if (a.w_b != nullptr) sb = fmaf(tb[R - r], u[r][e], sb);
+      for (int r = kMaxTaps - 1; r >= 0; --r) {       // tap taps - 1 - r reads the row r back; the oldest row first
+        if (r <= R) {
+          float wa[W];
+          load_vec<W>(a.taps_a + static_cast<long long>(R - r) * D + d, wa);
+#pragma unroll
+          for (int e = 0; e < W; ++e) oa[e] = fmaf(wa[e], u[r][e], oa[e]);
+          if (a.w_b != nullptr) {
+            float wb[W];
+            load_vec<W>(a.taps_b + static_cast<long long>(R - r) * D + d, wb);
+#pragma unroll
+            for (int e = 0; e < W; ++e) ob[e] = fmaf(wb[e], u[r][e], ob[e]);
           }
         }
-        oa[e] = a.w_a[d + e] * sa;
-        ob[e] = a.w_b != nullptr ? a.w_b[d + e] * sb : 0.0f;
+      }
+      {
+        float na[W];
+        load_vec<W>(a.w_a + d, na);
+#pragma unroll
+        for (int e = 0; e < W; ++e) oa[e] *= na[e];
+        if (a.w_b != nullptr) {
+          float nb[W];
+          load_vec<W>(a.w_b + d, nb);
+#pragma unroll
+          for (int e = 0; e < W; ++e) ob[e] *= nb[e];
+        }
       }
       store_vec(static_cast<T*>(a.out_a) + static_cast<long long>(t) * D + d, oa);
       if (a.w_b != nullptr) store_vec(static_cast<T*>(a.out_b) + static_cast<long long>(t) * D + d, ob);
@@ -685,9 +668,9 @@ TIE_API int tie_group_norm_taps(int dtype, float* x, const void* delta, const fl
   a.seq_of_row = seq_of_row, a.positions = positions, a.query_start = query_start, a.context_lens = context_lens;
   a.state_slots = state_slots;
   if (taps > 0) {
-    // tiles of 2 rows once that still gives every SM several blocks (larger tiles leave too few blocks in flight to hide
-    // the loads); 4 columns a thread where the groups allow
-    const int tile = tile_rows > 0 ? tile_rows : n >= 2 * 4 * 148 ? 2 : 1;
+    // tiles of 4 rows once that still gives every SM several blocks (measured: 1 to 4 rows differ little, 8 and more leave
+    // too few blocks in flight to hide the loads); 4 columns a thread where the groups allow
+    const int tile = tile_rows > 0 ? tile_rows : n >= 4 * 4 * 148 ? 4 : 1;
     TIE_REQUIRE(tile <= 64, "group_norm_taps: tiles of at most 64 rows, got %d", tile);
     const bool wide = dim % 4 == 0 && (dim / groups) % 4 == 0;
     const size_t tile_smem = (static_cast<size_t>(tile + taps - 1) * groups + 4 * tile) * sizeof(float);
@@ -707,7 +690,7 @@ TIE_API int tie_group_norm_taps(int dtype, float* x, const void* delta, const fl
     TIE_RETURN_LAUNCH("group_norm_taps");
   }
   const bool summed = taps == 0 && (delta != nullptr || part != nullptr);
-  const size_t smem = (static_cast<size_t>(taps > 0 ? taps : 1) * groups + (summed ? dim : 0)) * sizeof(float);
+  const size_t smem = (static_cast<size_t>(groups) + (summed ? dim : 0)) * sizeof(float);
   TIE_REQUIRE(smem <= 200 * 1024, "group_norm_taps: a row of %d columns does not fit shared memory", dim);
   if (dtype == TIE_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(group_norm_taps_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));

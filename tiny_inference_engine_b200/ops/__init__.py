@@ -1127,14 +1127,15 @@ def add_row_vector(x, vec) -> None:
 
 def group_norm_taps(x, groups: int, eps: float, w_a, out_a, w_b=None, out_b=None, taps_a=None, taps_b=None, ctx=None, unit=None,
                     ring=None, delta=None, rows=None, tile: int = 0) -> None:
-    """u = x / rms over each of `groups` equal parts of a row; out_a = w_a * (u_t + sum_j taps_a[:, j] u_(t - taps + 1 + j)) and
+    """u = x / rms over each of `groups` equal parts of a row; out_a = w_a * (u_t + sum_j taps_a[j] u_(t - taps + 1 + j)) (taps_a
+    float32 [taps, D]: tap j of every channel side by side) and
     likewise out_b (optional): a grouped RMS norm whose output passes h + conv(h), a causal convolution over time per channel.
     With taps, `ctx` gives the step's index arrays, `ring` [slots, taps - 1, D] float32 the unit rows of earlier steps (by
     position mod taps - 1) and `unit` [T, D] receives the rows that `parallel_finish` moves into the ring. Without taps it is the
     grouped norm alone: `delta` (tensor or SplitSum) is added to x first and `rows` gathers (x is then left as it is). `tile`:
     rows a block with taps (0: chosen by the number of rows; the result does not depend on it)."""
     T, D = x.shape
-    taps = 0 if taps_a is None else taps_a.shape[1]
+    taps = 0 if taps_a is None else taps_a.shape[0]
     _dev(x, w_a, w_b, out_a, out_b, taps_a, taps_b, unit, ring, rows)
     _need(x.dtype == torch.float32 and x.is_contiguous(), "group_norm_taps: x must be float32 contiguous")
     n = out_a.shape[0]
@@ -1145,8 +1146,8 @@ def group_norm_taps(x, groups: int, eps: float, w_a, out_a, w_b=None, out_b=None
         _need(w is None or (w.dtype == torch.float32 and w.numel() == D), "group_norm_taps: norm weights must be float32 [D]")
     _need((w_b is None) == (out_b is None), "group_norm_taps: the second output needs a weight and a buffer")
     for tw in (taps_a, taps_b):
-        _need(tw is None or (tw.dtype == torch.float32 and tw.shape == (D, taps) and tw.is_contiguous()),
-              "group_norm_taps: taps must be float32 [D, taps]")
+        _need(tw is None or (tw.dtype == torch.float32 and tw.shape == (taps, D) and tw.is_contiguous()),
+              "group_norm_taps: taps must be float32 [taps, D]")
     if rows is None:
         _need(n == T, "group_norm_taps: out must have x's rows")
     else:

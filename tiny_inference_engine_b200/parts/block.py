@@ -189,8 +189,9 @@ class ParallelBlock(Block):
             part.bind(get)
         f32 = lambda name: get(name).to(torch.float32).contiguous()
         if self.taps > 0:
-            self.taps_a = f32(self.prefix + self.conv_names[0])
-            self.taps_b = f32(self.prefix + self.conv_names[1]) if self.has_ffn else None
+            by_tap = lambda name: get(name).to(torch.float32).t().contiguous()      # [taps, hidden]: a tap of every channel side by side
+            self.taps_a = by_tap(self.prefix + self.conv_names[0])
+            self.taps_b = by_tap(self.prefix + self.conv_names[1]) if self.has_ffn else None
         if self.side_spec is not None:
             s = self.side_spec
             dim, at = int(s["dim"]), int(s["index"]) * int(s["dim"])
