@@ -387,7 +387,7 @@ def test_the_token_side_input_as_matrix_products(tmp_path, truth, name, dtype, m
     close(hs.in_portions("p", toks, [40, 3, 12, 1, 30, 11, 2]), want, dtype, f"{name} in portions")
 
 
-@pytest.mark.parametrize("shape", [(256, 16, 3), (36, 5, 1), (2048, 64, 2), (40, 8, 0)])
+@pytest.mark.parametrize("shape", [(256, 16, 3), (36, 5, 1), (2048, 64, 2), (40, 8, 0), (30, 6, 2)])
 def test_sublayer_sum_and_token_side_input_for_few_and_for_more_rows(shape):
     """x += mult * (a + b), the token side input and the ring update: a handful of rows (a thread-block cluster a row,
     many times over: the CTAs of a cluster read the row that one of them writes), some dozens of rows (a block a row)

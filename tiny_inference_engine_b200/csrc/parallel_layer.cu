@@ -543,14 +543,47 @@ static int launch_finish_cluster(const FinishArgs& a, cudaStream_t s) {
   TIE_RETURN_LAUNCH("parallel_finish");
 }
 
+// Four consecutive elements of a delta (idx a multiple of 4, the row width too).
+__device__ __forceinline__ void load4_as_float(const float* p, float (&v)[4]) { load_vec<4>(p, v); }
+__device__ __forceinline__ void load4_as_float(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 t = *reinterpret_cast<const uint2*>(p);
+  v[0] = __uint_as_float(t.x << 16), v[1] = __uint_as_float(t.x & 0xffff0000u);
+  v[2] = __uint_as_float(t.y << 16), v[3] = __uint_as_float(t.y & 0xffff0000u);
+}
 template <typename T>
+__device__ __forceinline__ void delta_at4(const Delta& d, long long idx, float (&y)[4]) {
+  y[0] = y[1] = y[2] = y[3] = 0.0f;
+  if (d.tensor != nullptr) {
+    load4_as_float(static_cast<const T*>(d.tensor) + idx, y);
+  } else if (d.part != nullptr) {
+    for (int z = 0; z < d.splits; ++z) {
+      float p[4];
+      load_vec<4>(d.part + z * d.part_stride + idx, p);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) y[e] += p[e];
+    }
+  }
+}
+
+// W = 4: four columns a thread (the row width and, with partial sums, their stride are multiples of 4).
+template <typename T, int W>
 __global__ void __launch_bounds__(256) parallel_sum_kernel(float* __restrict__ x, T* __restrict__ copy, int D, float mult, Delta da, Delta db) {
   pdl_sync();
   const long long base = static_cast<long long>(blockIdx.x) * D;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    const float v = x[base + d] + mult * (delta_at<T>(da, base + d) + delta_at<T>(db, base + d));
-    x[base + d] = v;
-    st(copy + base + d, v);
+  for (int d = threadIdx.x * W; d < D; d += blockDim.x * W) {
+    float v[W];
+    if constexpr (W == 4) {
+      float a[4], b[4];
+      load_vec<4>(x + base + d, v);
+      delta_at4<T>(da, base + d, a);
+      delta_at4<T>(db, base + d, b);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[e] += mult * (a[e] + b[e]);
+    } else {
+      v[0] = x[base + d] + mult * (delta_at<T>(da, base + d) + delta_at<T>(db, base + d));
+    }
+    store_vec(x + base + d, v);
+    store_vec(copy + base + d, v);
   }
 }
 
@@ -580,6 +613,7 @@ struct SideFinishArgs {
   const int* state_slots;
 };
 
+template <int W>
 __global__ void __launch_bounds__(256) side_finish_kernel(SideFinishArgs a) {
   pdl_sync();
   __shared__ float scratch[40];
@@ -587,10 +621,23 @@ __global__ void __launch_bounds__(256) side_finish_kernel(SideFinishArgs a) {
   const float* yr = a.y + static_cast<long long>(t) * D;
   float* xr = a.x + static_cast<long long>(t) * D;
   float ss = 0.0f;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) ss = fmaf(yr[d], yr[d], ss);
+  for (int d = threadIdx.x * W; d < D; d += blockDim.x * W) {
+    float y[W];
+    load_vec<W>(yr + d, y);
+#pragma unroll
+    for (int e = 0; e < W; ++e) ss = fmaf(y[e], y[e], ss);
+  }
   ss = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(ss / static_cast<float>(D) + a.eps);
-  for (int d = threadIdx.x; d < D; d += blockDim.x) xr[d] += a.mult * (yr[d] * inv) * a.w[d];
+  for (int d = threadIdx.x * W; d < D; d += blockDim.x * W) {
+    float y[W], x[W], w[W];
+    load_vec<W>(yr + d, y);
+    load_vec<W>(xr + d, x);
+    load_vec<W>(a.w + d, w);
+#pragma unroll
+    for (int e = 0; e < W; ++e) x[e] += a.mult * (y[e] * inv) * w[e];
+    store_vec(xr + d, x);
+  }
   if (a.R > 0) {
     const int s = a.seq_of_row[t];
     const int pos = a.positions[t], slot = a.state_slots[s];
@@ -746,10 +793,13 @@ TIE_API int tie_parallel_sum(int dtype, float* x, void* copy, int rows, int dim,
               "parallel_sum: give a delta or partial sums, not both");
   if (rows == 0) return kOk;
   const Delta da{delta_a, part_a, stride_a, splits_a}, db{delta_b, part_b, stride_b, splits_b};
+  const bool wide = dim % 4 == 0 && (part_a == nullptr || stride_a % 4 == 0) && (part_b == nullptr || stride_b % 4 == 0);
   if (dtype == TIE_F32) {
-    TIE_LAUNCH((parallel_sum_kernel<float>), rows, 256, 0, s, x, static_cast<float*>(copy), dim, mult, da, db);
+    if (wide) TIE_LAUNCH((parallel_sum_kernel<float, 4>), rows, 256, 0, s, x, static_cast<float*>(copy), dim, mult, da, db);
+    else TIE_LAUNCH((parallel_sum_kernel<float, 1>), rows, 256, 0, s, x, static_cast<float*>(copy), dim, mult, da, db);
   } else if (dtype == TIE_BF16) {
-    TIE_LAUNCH((parallel_sum_kernel<__nv_bfloat16>), rows, 256, 0, s, x, static_cast<__nv_bfloat16*>(copy), dim, mult, da, db);
+    if (wide) TIE_LAUNCH((parallel_sum_kernel<__nv_bfloat16, 4>), rows, 256, 0, s, x, static_cast<__nv_bfloat16*>(copy), dim, mult, da, db);
+    else TIE_LAUNCH((parallel_sum_kernel<__nv_bfloat16, 1>), rows, 256, 0, s, x, static_cast<__nv_bfloat16*>(copy), dim, mult, da, db);
   } else {
     set_error("parallel_sum: unknown dtype code %d", dtype);
     return kBadArgument;
@@ -786,6 +836,7 @@ TIE_API int tie_side_finish(float* x, const float* y, int rows, int dim, float m
                                  context_lens != nullptr && state_slots != nullptr), "side_finish: the ring needs the step's index arrays");
   if (rows == 0) return kOk;
   SideFinishArgs a{x, y, dim, mult, eps, w, unit, ring, ring_rows, seq_of_row, positions, context_lens, state_slots};
-  TIE_LAUNCH(side_finish_kernel, rows, 256, 0, s, a);
+  if (dim % 4 == 0) TIE_LAUNCH(side_finish_kernel<4>, rows, 256, 0, s, a);
+  else TIE_LAUNCH(side_finish_kernel<1>, rows, 256, 0, s, a);
   TIE_RETURN_LAUNCH("side_finish");
 }
