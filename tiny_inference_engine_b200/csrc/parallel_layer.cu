@@ -155,15 +155,19 @@ template <int W> __device__ __forceinline__ void load_vec(const float* p, float 
   }
 }
 
-// group_norm_taps with taps for `tile` consecutive rows a block: the norms of the tile's rows and of the taps - 1 rows
-// before it are computed once (a warp per row and group), then every row of the tile forms its outputs, W columns a
-// thread at a time. A row's numbers do not depend on the tile it falls into.
-template <typename T, int W>
+// group_norm_taps with TAPS taps for `tile` consecutive rows a block: the norms of the tile's rows and of the TAPS - 1
+// rows before it are computed once (a warp per row and group); then a thread owns W columns and walks down the tile's
+// rows with the unit values of the TAPS - 1 rows above in registers, so that x is read once a tile (plus the rows
+// above it) and the tap weights once a thread. A row whose predecessors are not in this step (another sequence above
+// it, or an earlier step) takes them from its request's ring, or zeros ahead of position 0. A row's numbers do not
+// depend on the tile it falls into.
+template <typename T, int W, int TAPS>
 __global__ void __launch_bounds__(256) group_norm_taps_tile_kernel(NormTapsArgs a, int tile) {
   pdl_sync();
   extern __shared__ float smem[];
+  constexpr int R = TAPS - 1, RR = R > 0 ? R : 1;
   float* inv = smem;                       // [(tile + R) * groups], row t0 - R first
-  const int D = a.D, R = a.taps - 1, G = a.groups;
+  const int D = a.D, G = a.groups;
   const int gsize = D / G;
   const int t0 = blockIdx.x * tile;
   const int nr = min(tile, a.n - t0);
@@ -194,68 +198,79 @@ __global__ void __launch_bounds__(256) group_norm_taps_tile_kernel(NormTapsArgs 
     meta[4 * j + 3] = R > 0 && pos >= a.context_lens[s] - R;
   }
   __syncthreads();
-  const int per_row = D / W;
-  for (int item = threadIdx.x; item < nr * per_row; item += blockDim.x) {
-    const int j = item / per_row, d = (item - j * per_row) * W;
-    const int t = t0 + j;
-    const int pos = meta[4 * j], first = meta[4 * j + 1], slot = meta[4 * j + 2];
-    const bool keep = meta[4 * j + 3] != 0;
-    const float* xr = a.x + static_cast<long long>(t) * D;
-    const float* my_inv = inv + (j + R) * G;
-    {
-      const int g = d / gsize;
-      float u[kMaxTaps][W];
-      load_vec<W>(xr + d, u[0]);
+  const bool two = a.w_b != nullptr;
+  for (int d = threadIdx.x * W; d < D; d += blockDim.x * W) {
+    const int g = d / gsize;
+    float wa[TAPS][W], wb[TAPS][W], na[W], nb[W];
 #pragma unroll
-      for (int e = 0; e < W; ++e) u[0][e] *= my_inv[g];
+    for (int k = 0; k < TAPS; ++k) {
+      load_vec<W>(a.taps_a + static_cast<long long>(k) * D + d, wa[k]);
+      if (two) load_vec<W>(a.taps_b + static_cast<long long>(k) * D + d, wb[k]);
+    }
+    load_vec<W>(a.w_a + d, na);
+    if (two) load_vec<W>(a.w_b + d, nb);
+    float win[RR][W];                      // win[r - 1]: the unit value of the row r above the current one
 #pragma unroll
-      for (int r = 1; r < kMaxTaps; ++r) {
-        if (r > R) break;
+    for (int r = 1; r <= R; ++r) {
+#pragma unroll
+      for (int e = 0; e < W; ++e) win[r - 1][e] = 0.0f;
+      if (t0 - r >= 0) {
+        load_vec<W>(a.x + static_cast<long long>(t0 - r) * D + d, win[r - 1]);
+        const float scale = inv[(R - r) * G + g];
+#pragma unroll
+        for (int e = 0; e < W; ++e) win[r - 1][e] *= scale;
+      }
+    }
+    for (int j = 0; j < nr; ++j) {
+      const int t = t0 + j;
+      const int pos = meta[4 * j], first = meta[4 * j + 1], slot = meta[4 * j + 2];
+      float u[TAPS][W];
+      load_vec<W>(a.x + static_cast<long long>(t) * D + d, u[0]);
+      const float scale = inv[(j + R) * G + g];
+#pragma unroll
+      for (int e = 0; e < W; ++e) u[0][e] *= scale;
+#pragma unroll
+      for (int r = 1; r <= R; ++r) {
         const int p = pos - r;
-#pragma unroll
-        for (int e = 0; e < W; ++e) u[r][e] = 0.0f;
         if (p >= first) {
-          load_vec<W>(xr + d - static_cast<long long>(r) * D, u[r]);
-          const float scale = my_inv[g - r * G];
 #pragma unroll
-          for (int e = 0; e < W; ++e) u[r][e] *= scale;
+          for (int e = 0; e < W; ++e) u[r][e] = win[r - 1][e];
         } else if (p >= 0 && slot >= 0) {
-          load_vec<W>(a.ring + (static_cast<long long>(slot) * R + p % R) * D + d, u[r]);
+          load_vec<W>(a.ring + (static_cast<long long>(slot) * R + p % RR) * D + d, u[r]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < W; ++e) u[r][e] = 0.0f;
         }
       }
       float oa[W], ob[W];
 #pragma unroll
       for (int e = 0; e < W; ++e) oa[e] = ob[e] = u[0][e];
 #pragma unroll
-      for (int r = kMaxTaps - 1; r >= 0; --r) {       // tap taps - 1 - r reads the row r back; the oldest row first
-        if (r <= R) {
-          float wa[W];
-          load_vec<W>(a.taps_a + static_cast<long long>(R - r) * D + d, wa);
+      for (int r = R; r >= 0; --r) {       // tap TAPS - 1 - r reads the row r back; the oldest row first
 #pragma unroll
-          for (int e = 0; e < W; ++e) oa[e] = fmaf(wa[e], u[r][e], oa[e]);
-          if (a.w_b != nullptr) {
-            float wb[W];
-            load_vec<W>(a.taps_b + static_cast<long long>(R - r) * D + d, wb);
-#pragma unroll
-            for (int e = 0; e < W; ++e) ob[e] = fmaf(wb[e], u[r][e], ob[e]);
-          }
+        for (int e = 0; e < W; ++e) {
+          oa[e] = fmaf(wa[R - r][e], u[r][e], oa[e]);
+          if (two) ob[e] = fmaf(wb[R - r][e], u[r][e], ob[e]);
         }
       }
-      {
-        float na[W];
-        load_vec<W>(a.w_a + d, na);
 #pragma unroll
-        for (int e = 0; e < W; ++e) oa[e] *= na[e];
-        if (a.w_b != nullptr) {
-          float nb[W];
-          load_vec<W>(a.w_b + d, nb);
-#pragma unroll
-          for (int e = 0; e < W; ++e) ob[e] *= nb[e];
-        }
-      }
+      for (int e = 0; e < W; ++e) oa[e] *= na[e];
       store_vec(static_cast<T*>(a.out_a) + static_cast<long long>(t) * D + d, oa);
-      if (a.w_b != nullptr) store_vec(static_cast<T*>(a.out_b) + static_cast<long long>(t) * D + d, ob);
-      if (keep) store_vec(a.unit + static_cast<long long>(t) * D + d, u[0]);
+      if (two) {
+#pragma unroll
+        for (int e = 0; e < W; ++e) ob[e] *= nb[e];
+        store_vec(static_cast<T*>(a.out_b) + static_cast<long long>(t) * D + d, ob);
+      }
+      if (meta[4 * j + 3] != 0) store_vec(a.unit + static_cast<long long>(t) * D + d, u[0]);
+#pragma unroll
+      for (int r = R; r >= 2; --r) {
+#pragma unroll
+        for (int e = 0; e < W; ++e) win[r - 1][e] = win[r - 2][e];
+      }
+      if (R > 0) {
+#pragma unroll
+        for (int e = 0; e < W; ++e) win[0][e] = u[0][e];
+      }
     }
   }
 }
@@ -715,24 +730,36 @@ TIE_API int tie_group_norm_taps(int dtype, float* x, const void* delta, const fl
   a.seq_of_row = seq_of_row, a.positions = positions, a.query_start = query_start, a.context_lens = context_lens;
   a.state_slots = state_slots;
   if (taps > 0) {
-    // tiles of 4 rows once that still gives every SM several blocks (measured: 1 to 4 rows differ little, 8 and more leave
-    // too few blocks in flight to hide the loads); 4 columns a thread where the groups allow
-    const int tile = tile_rows > 0 ? tile_rows : n >= 4 * 4 * 148 ? 4 : 1;
+    // rows a tile: as many (up to 8) as still leave every SM a block or two; measured at 2,048 rows of 2,048 columns with L2
+    // flushed, tiles of 1, 2, 4, 8, 16 rows take 41, 33, 27, 23, 29 us; 4 columns a thread where the groups allow
+    const int tile = tile_rows > 0 ? tile_rows : n >= 8 * 148 ? 8 : n >= 4 * 148 ? 4 : n >= 2 * 148 ? 2 : 1;
     TIE_REQUIRE(tile <= 64, "group_norm_taps: tiles of at most 64 rows, got %d", tile);
     const bool wide = dim % 4 == 0 && (dim / groups) % 4 == 0;
     const size_t tile_smem = (static_cast<size_t>(tile + taps - 1) * groups + 4 * tile) * sizeof(float);
     TIE_REQUIRE(tile_smem <= 48 * 1024, "group_norm_taps: %d groups are too many", groups);
-#define TIE_TAPS_CASE(TYPE, W) TIE_LAUNCH((group_norm_taps_tile_kernel<TYPE, W>), ceil_div(n, tile), 256, tile_smem, s, a, tile)
+#define TIE_TAPS_LAUNCH(TYPE, W, N) TIE_LAUNCH((group_norm_taps_tile_kernel<TYPE, W, N>), ceil_div(n, tile), 256, tile_smem, s, a, tile)
+#define TIE_TAPS_CASE(TYPE, W)                \
+  switch (taps) {                             \
+    case 1: TIE_TAPS_LAUNCH(TYPE, W, 1); break; \
+    case 2: TIE_TAPS_LAUNCH(TYPE, W, 2); break; \
+    case 3: TIE_TAPS_LAUNCH(TYPE, W, 3); break; \
+    case 4: TIE_TAPS_LAUNCH(TYPE, W, 4); break; \
+    case 5: TIE_TAPS_LAUNCH(TYPE, W, 5); break; \
+    case 6: TIE_TAPS_LAUNCH(TYPE, W, 6); break; \
+    case 7: TIE_TAPS_LAUNCH(TYPE, W, 7); break; \
+    default: TIE_TAPS_LAUNCH(TYPE, W, 8); break; \
+  }
     if (dtype == TIE_F32) {
-      if (wide) TIE_TAPS_CASE(float, 4);
-      else TIE_TAPS_CASE(float, 1);
+      if (wide) TIE_TAPS_CASE(float, 4)
+      else TIE_TAPS_CASE(float, 1)
     } else if (dtype == TIE_BF16) {
-      if (wide) TIE_TAPS_CASE(__nv_bfloat16, 4);
-      else TIE_TAPS_CASE(__nv_bfloat16, 1);
+      if (wide) TIE_TAPS_CASE(__nv_bfloat16, 4)
+      else TIE_TAPS_CASE(__nv_bfloat16, 1)
     } else {
       set_error("group_norm_taps: unknown dtype code %d", dtype);
       return kBadArgument;
     }
+#undef TIE_TAPS_LAUNCH
 #undef TIE_TAPS_CASE
     TIE_RETURN_LAUNCH("group_norm_taps");
   }
