@@ -41,6 +41,29 @@ struct AttnArgs {
   int v_dim;                // size of a value head (and of an output head); keys and queries have head_dim
   int v_ld;                 // elements between value rows; 0: v_dim. With the key plane given as the value plane too
                             // and v_ld = head_dim, a value is the first v_dim elements of its key (a latent cache).
+  // Score maps over slices of wider key rows (all zero: the plain attention above). A key row holds k_ld elements, and
+  // query head h reads the head_dim of them that start at ((h / sub_div) % sub_count) * head_dim: two score maps a head
+  // over one value (sub_div 1, sub_count 2), or all kv heads' keys in one row so that every query head weights the
+  // values of every kv head (sub_div = query heads per kv head, sub_count = kv heads, one cached head).
+  int k_ld;                 // elements between key rows; 0: head_dim
+  int sub_div, sub_count;
+  int chunk;                // > 0: a position sees the keys of its own chunk of this many positions (counted from 0) only
+  float softcap;            // > 0: score <- softcap * tanh(score / softcap)
+  const float* r1;          // [q_heads] or null: score -= r1[h] * ln(1 + r2[h] * (position - key position))
+  const float* r2;
+  int out_f32;              // the output rows are float whatever the storage type
+};
+
+// The first key that position `pos` sees.
+__device__ __forceinline__ int first_visible(int pos, int window, int chunk) {
+  if (chunk > 0) return pos / chunk * chunk;
+  return window > 0 ? max(0, pos - window + 1) : 0;
+}
+
+// What a score passes on its way to the softmax beside the scale: a cap and a bias that grows with the distance.
+struct ScoreShape {
+  float softcap, r1, r2;
+  int pos;                  // the query's position
 };
 
 // One warp: online softmax over keys [lo, hi] of one (query vector, kv head).
@@ -50,7 +73,9 @@ template <typename T, int DPL>
 __device__ __forceinline__ void attend_range(const float* __restrict__ qs, const T* __restrict__ kc,
                                              const T* __restrict__ vc, const int* __restrict__ table, int kvh,
                                              int kv_heads, int head_dim, int v_dim, int v_ld, int page_size, float scale,
-                                             int lo, int hi, float& m, float& l, float (&acc)[DPL]) {
+                                             int lo, int hi, float& m, float& l, float (&acc)[DPL], int k_ld = 0, int k_off = 0,
+                                             const ScoreShape shape = ScoreShape{0.0f, 0.0f, 0.0f, 0}) {
+  if (k_ld == 0) k_ld = head_dim;
   constexpr int V = Vec16<T>::N;
   const int lane = threadIdx.x & 31;
   const int d0 = lane * DPL;
@@ -62,9 +87,9 @@ __device__ __forceinline__ void attend_range(const float* __restrict__ qs, const
     if (valid) {
       const int page = table[j / page_size];
       row = (page * kv_heads + kvh) * page_size + j % page_size;
-      const T* kr = kc + static_cast<long long>(row) * head_dim;
+      const T* kr = kc + static_cast<long long>(row) * k_ld + k_off;
       float dot = 0.0f;
-      if (head_dim % V == 0) {      // rows of whole 16-byte pieces
+      if (head_dim % V == 0 && k_ld % V == 0) {      // rows of whole 16-byte pieces
         for (int d = 0; d < head_dim; d += V) {
           Vec16<T> kv;
           kv.load(kr + d);
@@ -75,6 +100,8 @@ __device__ __forceinline__ void attend_range(const float* __restrict__ qs, const
         for (int d = 0; d < head_dim; ++d) dot = fmaf(qs[d], ld(kr + d), dot);
       }
       s = scale * dot;
+      if (shape.softcap > 0.0f) s = shape.softcap * tanhf(s / shape.softcap);
+      if (shape.r1 != 0.0f) s -= shape.r1 * log1pf(shape.r2 * static_cast<float>(shape.pos - j));
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float corr = expf(m - m_new);  // m = -inf at the start gives 0
@@ -97,6 +124,14 @@ __device__ __forceinline__ void attend_range(const float* __restrict__ qs, const
   }
 }
 
+__device__ __forceinline__ int key_offset(const AttnArgs& a, int h) {
+  return a.sub_count > 1 ? ((h / a.sub_div) % a.sub_count) * a.head_dim : 0;
+}
+
+__device__ __forceinline__ ScoreShape score_shape(const AttnArgs& a, int h, int pos) {
+  return ScoreShape{a.softcap, a.r1 ? a.r1[h] : 0.0f, a.r1 ? a.r2[h] : 0.0f, pos};
+}
+
 template <typename T, int DPL>
 __global__ void __launch_bounds__(128) attention_rows_kernel(AttnArgs a) {
   pdl_sync();
@@ -109,7 +144,7 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(AttnArgs a) {
   const int s = a.seq_of_row[t];
   const int qs0 = a.query_start[s], qs1 = a.query_start[s + 1];
   const int pos = a.context_lens[s] - (qs1 - qs0) + (t - qs0);
-  const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+  const int lo = first_visible(pos, a.window, a.chunk);
   const int kvh = h / (a.q_heads / a.kv_heads);
 
   float* qs = smem + warp * a.head_dim;
@@ -120,14 +155,18 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(AttnArgs a) {
   float m = -INFINITY, l = 0.0f, acc[DPL] = {};
   attend_range<T, DPL>(qs, static_cast<const T*>(a.k_cache), static_cast<const T*>(a.v_cache),
                        a.block_tables + static_cast<long long>(s) * a.max_blocks, kvh, a.kv_heads, a.head_dim,
-                       a.v_dim, a.v_ld ? a.v_ld : a.v_dim, a.page_size, a.scale, lo, pos, m, l, acc);
+                       a.v_dim, a.v_ld ? a.v_ld : a.v_dim, a.page_size, a.scale, lo, pos, m, l, acc, a.k_ld, key_offset(a, h),
+                       score_shape(a, h, pos));
   const int d0 = lane * DPL;
   if (d0 < a.v_dim) {
-    T* o = static_cast<T*>(a.out) + (static_cast<long long>(t) * a.q_heads + h) * a.v_dim + d0;
+    const long long at = (static_cast<long long>(t) * a.q_heads + h) * a.v_dim + d0;
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;  // no keys (a padding row): zeros
 #pragma unroll
     for (int e = 0; e < DPL; ++e)
-      if (d0 + e < a.v_dim) st(o + e, acc[e] * inv);
+      if (d0 + e < a.v_dim) {
+        if (a.out_f32) static_cast<float*>(a.out)[at + e] = acc[e] * inv;
+        else st(static_cast<T*>(a.out) + at + e, acc[e] * inv);
+      }
   }
 }
 
@@ -147,7 +186,7 @@ __global__ void __launch_bounds__(128) attention_split_kernel(AttnArgs a, const 
   const int s = seq_list[li];
   const int t = a.query_start[s];
   const int pos = a.context_lens[s] - 1;
-  const int lo0 = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+  const int lo0 = first_visible(pos, a.window, a.chunk);
   const int lo = lo0 + split * split_keys;
   if (lo > pos) return;  // this sequence has fewer splits
   // The last split takes whatever is left, so that a context longer than max_splits * split_keys (a caller
@@ -163,7 +202,8 @@ __global__ void __launch_bounds__(128) attention_split_kernel(AttnArgs a, const 
   float m = -INFINITY, l = 0.0f, acc[DPL] = {};
   attend_range<T, DPL>(qs, static_cast<const T*>(a.k_cache), static_cast<const T*>(a.v_cache),
                        a.block_tables + static_cast<long long>(s) * a.max_blocks, kvh, a.kv_heads, a.head_dim,
-                       a.v_dim, a.v_ld ? a.v_ld : a.v_dim, a.page_size, a.scale, lo, hi, m, l, acc);
+                       a.v_dim, a.v_ld ? a.v_ld : a.v_dim, a.page_size, a.scale, lo, hi, m, l, acc, a.k_ld, key_offset(a, h),
+                       score_shape(a, h, pos));
   float* dst = scratch + ((static_cast<long long>(li) * a.q_heads + h) * max_splits + split) * (a.v_dim + 2);
   const int d0 = lane * DPL;
   if (d0 < a.v_dim) {
@@ -195,12 +235,17 @@ __global__ void __launch_bounds__(kMergeThreads) attention_merge_kernel(AttnArgs
   const int s = seq_list[li];
   const int t = a.query_start[s];
   const int pos = a.context_lens[s] - 1;
-  T* o = static_cast<T*>(a.out) + (static_cast<long long>(t) * a.q_heads + h) * a.head_dim;
+  const long long at = (static_cast<long long>(t) * a.q_heads + h) * a.head_dim;
+  T* o = static_cast<T*>(a.out) + at;
+  float* of = static_cast<float*>(a.out) + at;
   if (pos < 0) {  // a padding sequence: no keys, zeros
-    for (int d = threadIdx.x; d < a.head_dim; d += kMergeThreads) st(o + d, 0.0f);
+    for (int d = threadIdx.x; d < a.head_dim; d += kMergeThreads) {
+      if (a.out_f32) of[d] = 0.0f;
+      else st(o + d, 0.0f);
+    }
     return;
   }
-  const int lo0 = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+  const int lo0 = first_visible(pos, a.window, a.chunk);
   const int splits = min((pos - lo0) / split_keys + 1, max_splits);   // the last one took the rest (split kernels)
   const int stride = a.head_dim + 2;
   const float* src = scratch + (static_cast<long long>(li) * a.q_heads + h) * max_splits * stride;
@@ -221,7 +266,8 @@ __global__ void __launch_bounds__(kMergeThreads) attention_merge_kernel(AttnArgs
   for (int d = threadIdx.x; d < a.head_dim; d += kMergeThreads) {
     float acc = 0.0f;
     for (int i = 0; i < splits; ++i) acc = fmaf(src[i * stride + d], weight[i], acc);
-    st(o + d, acc * inv_l);
+    if (a.out_f32) of[d] = acc * inv_l;
+    else st(o + d, acc * inv_l);
   }
 }
 
@@ -253,7 +299,8 @@ int launch_attention(const AttnArgs& a, const int* row_seq_unused, const int* se
   else if (dpl <= 2) TIE_ATTN_CASE(2);
   else if (dpl <= 4) TIE_ATTN_CASE(4);
   else if (dpl <= 8) TIE_ATTN_CASE(8);
-  else TIE_ATTN_CASE(16);
+  else if (dpl <= 16) TIE_ATTN_CASE(16);
+  else TIE_ATTN_CASE(32);
 #undef TIE_ATTN_CASE
   TIE_RETURN_LAUNCH("paged_attention_simt");
 }
@@ -274,7 +321,7 @@ static int check_attn(const AttnArgs& a, bool any_size = false) {
     TIE_REQUIRE(a.head_dim <= 256 || a.head_dim % 16 == 0, "attention: head_dim %d above 256 must be a multiple of 16",
                 a.head_dim);
   }
-  TIE_REQUIRE(a.v_dim > 0 && a.v_dim <= 512, "attention: value heads of %d (1 to 512)", a.v_dim);
+  TIE_REQUIRE(a.v_dim > 0 && a.v_dim <= (any_size ? 1024 : 512), "attention: value heads of %d (1 to %d)", a.v_dim, any_size ? 1024 : 512);
   TIE_REQUIRE(a.page_size > 0 && a.max_blocks > 0, "attention: bad page geometry");
   TIE_REQUIRE(a.window >= 0, "attention: negative window");
   return kOk;
@@ -366,6 +413,49 @@ TIE_API int tie_attention_split_dv(int dtype, const void* q, long long q_stride,
   const AttnArgs a{q, k_cache, v_cache, out, nullptr, query_start, context_lens, block_tables, q_stride, max_blocks,
                    0, seqs, q_heads, kv_heads, head_dim, page_size, window, scale, v_dim, v_ld};
   TIE_REQUIRE(v_ld == 0 || v_ld >= v_dim, "attention: value rows %d apart are shorter than a value head of %d", v_ld, v_dim);
+  if (const int st = check_attn(a, true)) return st;
+  TIE_REQUIRE(split_keys > 0 && max_splits > 0 && max_splits <= kMergeMaxSplits && scratch != nullptr,
+              "attention split: bad split geometry (at most %d splits)", kMergeMaxSplits);
+  if (dtype == TIE_F32) return launch_attention<float>(a, nullptr, seq_list, n_list, split_keys, max_splits, scratch, 0, s);
+  if (dtype == TIE_BF16)
+    return launch_attention<__nv_bfloat16>(a, nullptr, seq_list, n_list, split_keys, max_splits, scratch, 0, s);
+  set_error("attention: unknown dtype code %d", dtype);
+  return kBadArgument;
+}
+
+// Score maps over slices of wider key rows (the fields of AttnArgs behind v_ld): the planes are
+// [pages, kv_heads, page_size, k_ld] and [pages, kv_heads, page_size, v_dim]; query head h reads kv head
+// h / (q_heads / kv_heads) and, of its key row, the head_dim elements from ((h / sub_div) % sub_count) * head_dim;
+// its softmax weights meet the whole value row. Chunks, a cap on the scores and a bias by the logarithm of the
+// distance are options. The output rows [T, q_heads * v_dim] are float.
+TIE_API int tie_attention_maps_rows(int dtype, const void* q, long long q_stride, const void* k_cache, const void* v_cache,
+                                    float* out, const int* seq_of_row, const int* query_start, const int* context_lens,
+                                    const int* block_tables, int max_blocks, int rows, int seqs, int q_heads, int kv_heads,
+                                    int head_dim, int k_ld, int sub_div, int sub_count, int v_dim, int page_size, int window,
+                                    int chunk, float scale, float softcap, const float* r1, const float* r2, cudaStream_t s) {
+  const AttnArgs a{q, k_cache, v_cache, out, seq_of_row, query_start, context_lens, block_tables, q_stride, max_blocks,
+                   rows, seqs, q_heads, kv_heads, head_dim, page_size, window, scale, v_dim, 0, k_ld, sub_div, sub_count,
+                   chunk, softcap, r1, r2, 1};
+  TIE_REQUIRE(sub_div > 0 && sub_count > 0 && k_ld >= sub_count * head_dim && chunk >= 0 && (r1 == nullptr) == (r2 == nullptr),
+              "attention maps: %d slices of %d do not fit key rows of %d", sub_count, head_dim, k_ld);
+  if (const int st = check_attn(a, true)) return st;
+  if (dtype == TIE_F32) return launch_attention<float>(a, nullptr, nullptr, 0, 0, 0, nullptr, 1, s);
+  if (dtype == TIE_BF16) return launch_attention<__nv_bfloat16>(a, nullptr, nullptr, 0, 0, 0, nullptr, 1, s);
+  set_error("attention: unknown dtype code %d", dtype);
+  return kBadArgument;
+}
+
+TIE_API int tie_attention_maps_split(int dtype, const void* q, long long q_stride, const void* k_cache, const void* v_cache,
+                                     float* out, const int* query_start, const int* context_lens, const int* block_tables,
+                                     int max_blocks, int seqs, int q_heads, int kv_heads, int head_dim, int k_ld, int sub_div,
+                                     int sub_count, int v_dim, int page_size, int window, int chunk, float scale, float softcap,
+                                     const float* r1, const float* r2, const int* seq_list, int n_list, int split_keys,
+                                     int max_splits, float* scratch, cudaStream_t s) {
+  const AttnArgs a{q, k_cache, v_cache, out, nullptr, query_start, context_lens, block_tables, q_stride, max_blocks,
+                   0, seqs, q_heads, kv_heads, head_dim, page_size, window, scale, v_dim, 0, k_ld, sub_div, sub_count,
+                   chunk, softcap, r1, r2, 1};
+  TIE_REQUIRE(sub_div > 0 && sub_count > 0 && k_ld >= sub_count * head_dim && chunk >= 0 && (r1 == nullptr) == (r2 == nullptr),
+              "attention maps: %d slices of %d do not fit key rows of %d", sub_count, head_dim, k_ld);
   if (const int st = check_attn(a, true)) return st;
   TIE_REQUIRE(split_keys > 0 && max_splits > 0 && max_splits <= kMergeMaxSplits && scratch != nullptr,
               "attention split: bad split geometry (at most %d splits)", kMergeMaxSplits);

@@ -126,13 +126,15 @@ __device__ __forceinline__ int delta_row(int r, int lane) { return (r >> 2) * (4
 // against q of the decayed state, and k . q beside them), three shuffle steps for the three, and the update: with
 // d1 = (gS)^T k and d2 = (gS)^T q, u = beta (v - d1) and the read-out of the updated state is o = d2 + (k . q) u.
 // RMAX: key channels a lane may hold (dim <= LANES * RMAX).
-template <typename T, int RMAX, int LANES, bool PLAIN>
+// BONUS (a specialization of the plain mode): the token reads the state as the token before left it and sees its own
+// write through a weight per key channel, o = S^T q + (sum_c bonus[h, c] k_c q_c) u, and only then S <- diag(decay) S + k u^T.
+template <typename T, int RMAX, int LANES, bool PLAIN, bool BONUS = false>
 __global__ void __launch_bounds__(LANES * kDeltaCols) delta_rule_kernel(
     const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vn, const float* __restrict__ beta,
     const float* __restrict__ decay, long long decay_stride, float* __restrict__ state, long long state_stride,
     long long conv_state_off, const T* __restrict__ proj, long long proj_stride, int q_off, int k_off, int v_off,
     const int* __restrict__ query_start, const int* __restrict__ state_slots, DeltaShape sh, int chunk,
-    float* __restrict__ out, int decay_per_head) {
+    float* __restrict__ out, int decay_per_head, const float* __restrict__ bonus = nullptr) {
   pdl_sync();
   extern __shared__ float smem[];
   const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * kDeltaCols;
@@ -218,7 +220,8 @@ __global__ void __launch_bounds__(LANES * kDeltaCols) delta_rule_kernel(
       // k . q of a token is the same for every column: once a chunk, a warp a token, instead of once a column
       for (int tc = warp; tc < cn; tc += static_cast<int>(blockDim.x >> 5)) {
         float dot = 0.0f;
-        for (int d = lane; d < dim; d += 32) dot = fmaf(kb[tc * dim + d], qb[tc * dim + d], dot);
+        for (int d = lane; d < dim; d += 32)
+          dot = fmaf(BONUS ? kb[tc * dim + d] * bonus[h * dim + d] : kb[tc * dim + d], qb[tc * dim + d], dot);
         dot = warp_sum(dot);
         if (lane == 0) kq[tc] = dot;
       }
@@ -256,15 +259,17 @@ __global__ void __launch_bounds__(LANES * kDeltaCols) delta_rule_kernel(
         }
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float sv = sreg[4 * q4 + e] * gg[e];
+          const float s0 = sreg[4 * q4 + e];
+          const float sv = s0 * gg[e];
+          const float seen = BONUS ? s0 : sv;     // what the read-out sees of the state: before or after the decay
           sreg[4 * q4 + e] = sv;
           kreg[4 * q4 + e] = kk[e];
           if (e & 1) {
             if (!PLAIN) d1b = fmaf(kk[e], sv, d1b);
-            d2b = fmaf(qq[e], sv, d2b);
+            d2b = fmaf(qq[e], seen, d2b);
           } else {
             if (!PLAIN) d1a = fmaf(kk[e], sv, d1a);
-            d2a = fmaf(qq[e], sv, d2a);
+            d2a = fmaf(qq[e], seen, d2a);
           }
           if (!PLAIN) d3 = fmaf(kk[e], qq[e], d3);
         }
@@ -376,7 +381,7 @@ static int launch_delta_rule(const float* qn, const float* kn, const float* vn, 
                              long long decay_stride, float* state, long long state_stride, long long conv_state_off,
                              const void* proj, long long proj_stride, int q_off, int k_off, int v_off,
                              const int* query_start, const int* state_slots, int seqs, const DeltaShape& sh, float* out,
-                             int plain, int decay_per_head, cudaStream_t s) {
+                             int plain, int decay_per_head, cudaStream_t s, const float* bonus = nullptr) {
   const dim3 grid(seqs, sh.heads, ceil_div(sh.vdim, kDeltaCols));
   const int per_token = 3 * sh.dim + kDeltaCols + 1;
   int chunk = (44 * 1024 / static_cast<int>(sizeof(float))) / (2 * per_token);      // two buffers
@@ -388,14 +393,18 @@ static int launch_delta_rule(const float* qn, const float* kn, const float* vn, 
   const T* p = static_cast<const T*>(proj);
 #define TIE_DELTA_CASE(R, LANES)                                                                                          \
   do {                                                                                                                    \
-    if (plain)                                                                                                            \
+    if (plain && bonus)                                                                                                   \
+      tie::launch_kernel(delta_rule_kernel<T, R, LANES, true, true>, grid, dim3(LANES * kDeltaCols), smem, s, qn, kn, vn, beta, decay, \
+                         decay_stride, state, state_stride, conv_state_off, p, proj_stride, q_off, k_off, v_off, query_start,   \
+                         state_slots, sh, chunk, out, decay_per_head, bonus);                                             \
+    else if (plain)                                                                                                       \
       tie::launch_kernel(delta_rule_kernel<T, R, LANES, true>, grid, dim3(LANES * kDeltaCols), smem, s, qn, kn, vn, beta, decay, \
                          decay_stride, state, state_stride, conv_state_off, p, proj_stride, q_off, k_off, v_off, query_start,   \
-                         state_slots, sh, chunk, out, decay_per_head);                                                    \
+                         state_slots, sh, chunk, out, decay_per_head, nullptr);                                           \
     else                                                                                                                  \
       tie::launch_kernel(delta_rule_kernel<T, R, LANES, false>, grid, dim3(LANES * kDeltaCols), smem, s, qn, kn, vn, beta, decay, \
                          decay_stride, state, state_stride, conv_state_off, p, proj_stride, q_off, k_off, v_off, query_start,   \
-                         state_slots, sh, chunk, out, decay_per_head);                                                    \
+                         state_slots, sh, chunk, out, decay_per_head, nullptr);                                           \
   } while (0)
   if (sh.dim <= 32) TIE_DELTA_CASE(4, 8);
   else if (sh.dim <= 64) TIE_DELTA_CASE(4, 16);
@@ -441,4 +450,26 @@ TIE_API int tie_delta_out(int dtype, const float* o, const float* gate, long lon
     return kBadArgument;
   }
   TIE_RETURN_LAUNCH("delta_out");
+}
+
+// The plain recurrence read before it is written, with a weight per head and key channel on the token's own write
+// (`bonus`, float [heads * dim]): o_t = (S + diag(bonus) k_t u_t^T)^T q_t, then S <- diag(decay_t) S + k_t u_t^T.
+TIE_API int tie_delta_rule_bonus(int dtype, const float* qn, const float* kn, const float* vn, const float* beta,
+                                 const float* decay, long long decay_stride, float* state, long long state_stride,
+                                 long long conv_state_off, const void* proj, long long proj_stride, int q_off, int k_off,
+                                 int v_off, const int* query_start, const int* state_slots, int seqs, int heads,
+                                 int kv_heads, int dim, int vdim, int taps, float* out, const float* bonus, cudaStream_t s) {
+  const DeltaShape sh{heads, kv_heads, dim, vdim, taps};
+  if (const int st_ = check_delta(sh)) return st_;
+  if (seqs <= 0) return kOk;
+  TIE_REQUIRE(bonus != nullptr && heads == kv_heads, "delta_rule_bonus: a weight per head and key channel, and a key head per head");
+  TIE_REQUIRE(seqs <= 65535 * 32 && heads <= 65535, "delta_rule: %d sequences x %d heads exceed the grid", seqs, heads);
+  if (dtype == TIE_F32)
+    return launch_delta_rule<float>(qn, kn, vn, beta, decay, decay_stride, state, state_stride, conv_state_off, proj, proj_stride,
+                                    q_off, k_off, v_off, query_start, state_slots, seqs, sh, out, 1, 0, s, bonus);
+  if (dtype == TIE_BF16)
+    return launch_delta_rule<__nv_bfloat16>(qn, kn, vn, beta, decay, decay_stride, state, state_stride, conv_state_off, proj,
+                                            proj_stride, q_off, k_off, v_off, query_start, state_slots, seqs, sh, out, 1, 0, s, bonus);
+  set_error("unknown dtype code %d", dtype);
+  return kBadArgument;
 }

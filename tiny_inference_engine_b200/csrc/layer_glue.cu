@@ -152,6 +152,17 @@ __global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ out
   st(out + i, (g / (1.0f + expf(-slope * g))) * (u + up_shift));
 }
 
+// One hidden layer's activation in two branches that meet at zero with the slope 1/2:
+//   z > 0: c_pos z^2 + z / 2;   z <= 0: c_neg (exp(z) - 1 - z) + z / 2.
+template <typename T>
+__global__ void two_branch_unit_kernel(const T* __restrict__ z, T* __restrict__ out, long long total, float c_pos, float c_neg) {
+  pdl_sync();
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const float v = ld(z + i);
+  st(out + i, v > 0.0f ? fmaf(c_pos * v, v, 0.5f * v) : fmaf(c_neg, expm1f(v) - v, 0.5f * v));
+}
+
 template <typename T>
 __global__ void sigmoid_gate_mul_kernel(T* __restrict__ y, long long y_stride, const T* __restrict__ gate,
                                         long long gate_stride, int width, long long total) {
@@ -283,6 +294,22 @@ TIE_API int tie_glu_clamped(int dtype, const void* gu, void* out, int tokens, in
     return kBadArgument;
   }
   TIE_RETURN_LAUNCH("glu_clamped");
+}
+
+TIE_API int tie_two_branch_unit(int dtype, const void* z, void* out, long long total, float c_pos, float c_neg, cudaStream_t s) {
+  TIE_REQUIRE(total >= 0, "two_branch_unit: bad size");
+  if (total == 0) return kOk;
+  if (dtype == TIE_F32) {
+    TIE_LAUNCH((two_branch_unit_kernel<float>), ceil_div(total, 256), 256, 0, s, static_cast<const float*>(z), static_cast<float*>(out), total,
+               c_pos, c_neg);
+  } else if (dtype == TIE_BF16) {
+    TIE_LAUNCH((two_branch_unit_kernel<__nv_bfloat16>), ceil_div(total, 256), 256, 0, s, static_cast<const __nv_bfloat16*>(z),
+               static_cast<__nv_bfloat16*>(out), total, c_pos, c_neg);
+  } else {
+    set_error("unknown dtype code %d", dtype);
+    return kBadArgument;
+  }
+  TIE_RETURN_LAUNCH("two_branch_unit");
 }
 
 TIE_API int tie_sigmoid_gate_mul(int dtype, void* y, long long y_stride, const void* gate, long long gate_stride, int tokens,

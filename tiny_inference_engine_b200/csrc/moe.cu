@@ -44,7 +44,7 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, long long ld_logits, int tokens,
                                                         int experts, int top, int groups, int keep, int score_fn,
                                                         const float* __restrict__ correction, int group_top, int renorm,
-                                                        int* __restrict__ ids, float* __restrict__ weights) {
+                                                        float weight_scale, int* __restrict__ ids, float* __restrict__ weights) {
   pdl_sync();
   extern __shared__ float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -130,7 +130,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
   }
   if (lane < top) {
     ids[t * top + lane] = mine_e;
-    weights[t * top + lane] = renorm ? mine_w / (total + 1e-20f) : mine_w;
+    weights[t * top + lane] = (renorm ? mine_w / (total + 1e-20f) : mine_w) * weight_scale;     // the scale is a constant of the layer
   }
 }
 
@@ -406,8 +406,8 @@ TIE_API int tie_moe_combine(int dtype, const void* y, const int* sorted, const i
 }
 
 TIE_API int tie_moe_route(const float* logits, long long ld_logits, int tokens, int experts, int top, int groups, int keep,
-                          int score_fn, const float* correction, int group_top, int renorm, int* ids, float* weights,
-                          cudaStream_t s) {
+                          int score_fn, const float* correction, int group_top, int renorm, float weight_scale, int* ids,
+                          float* weights, cudaStream_t s) {
   TIE_REQUIRE((score_fn == 0 || score_fn == 1) && group_top >= 1, "moe_route: score function %d, %d members a group's score",
               score_fn, group_top);
   TIE_REQUIRE(experts > 0 && top > 0 && top <= 32 && top <= experts && groups > 0 && experts % groups == 0 && keep > 0 &&
@@ -417,7 +417,7 @@ TIE_API int tie_moe_route(const float* logits, long long ld_logits, int tokens, 
   const size_t smem = 4 * sizeof(float) * (2 * experts + 2 * groups);
   TIE_REQUIRE(smem <= 48 * 1024, "moe_route: %d experts exceed the kernel's shared memory", experts);
   TIE_LAUNCH(moe_route_kernel, ceil_div(tokens, 4), 128, smem, s, logits, ld_logits, tokens, experts, top, groups, keep, score_fn,
-             correction, group_top, renorm, ids, weights);
+             correction, group_top, renorm, weight_scale, ids, weights);
   TIE_RETURN_LAUNCH("moe_route");
 }
 

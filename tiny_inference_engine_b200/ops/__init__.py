@@ -984,11 +984,11 @@ ROUTE_SOFTMAX, ROUTE_SIGMOID = 0, 1
 
 
 def moe_route(logits, top: int, groups: int, keep: int, ids, weights, score_fn: int = ROUTE_SOFTMAX, correction=None,
-              group_top: int = 1, renorm: bool = True) -> None:
+              group_top: int = 1, renorm: bool = True, weight_scale: float = 1.0) -> None:
     """Per token: scores over all experts (`score_fn`: a softmax over the experts, or a sigmoid each); choice scores = scores +
     `correction` (float32 [E], optional); the `keep` best of `groups` equal blocks of consecutive experts (a group counts as the
     sum of its `group_top` largest choice scores: 1 = its best member); the `top` best experts of those by choice score. ids
-    int32 [T, top], weights float32 [T, top] = the chosen experts' scores, over their sum (+ 1e-20) with `renorm`."""
+    int32 [T, top], weights float32 [T, top] = the chosen experts' scores, over their sum (+ 1e-20) with `renorm`, times `weight_scale`."""
     _dev(logits, ids, weights, correction)
     T, E = logits.shape
     _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "moe_route: logits must be float32 rows")
@@ -997,7 +997,7 @@ def moe_route(logits, top: int, groups: int, keep: int, ids, weights, score_fn: 
     _need(correction is None or (correction.dtype == torch.float32 and correction.numel() == E and correction.is_contiguous()),
           "moe_route: the correction must be float32 [experts]")
     call("tie_moe_route", logits.data_ptr(), logits.stride(0), T, E, top, groups, keep, int(score_fn), _ptr(correction),
-         int(group_top), int(bool(renorm)), ids.data_ptr(), weights.data_ptr(), _stream())
+         int(group_top), int(bool(renorm)), float(weight_scale), ids.data_ptr(), weights.data_ptr(), _stream())
 
 
 def moe_max_tiles(pairs: int, experts: int, block_m: int) -> int:
@@ -1309,3 +1309,230 @@ def attention_mixed_tc(q, k_cache, v_cache, out, mix, query_start, context_lens,
     if split and n_seqs > 0:
         call("tie_attention_merge", dtype_code(out), out.data_ptr(), query_start.data_ptr(), context_lens.data_ptr(), heads, vdim,
              0, seq_list.data_ptr(), n_seqs, split_keys, max_splits, scratch.data_ptr(), _stream())
+
+
+# -- a norm without statistics and a sinusoid on the embedding (csrc/tanh_norm.cu)
+
+class ScaledSum:
+    """Sublayer outputs that join the residual stream together, each with a factor: sum_i scale_i * term_i, a term a
+    tensor [T, D] in the compute dtype or a SplitSum. Norms that say `takes_scaled_sum` add the terms in float32 while
+    they read them; `materialize` adds them into a tensor for everyone else."""
+
+    def __init__(self, terms):
+        self.terms = [(t, float(c)) for t, c in terms if t is not None]
+        if not 1 <= len(self.terms) <= 2:
+            raise InvalidArgument(f"a scaled sum has one or two terms, got {len(self.terms)}")
+
+    def materialize(self, out: torch.Tensor) -> torch.Tensor:
+        acc = torch.zeros(out.shape, dtype=torch.float32, device=out.device)      # off the product path: toy parts and tests only
+        for t, c in self.terms:
+            if isinstance(t, SplitSum):
+                t = t.partial[:t.splits * t.stride].view(t.splits, t.M, t.N).sum(dim=0)
+            acc += c * t.float()
+        out.copy_(acc)
+        return out
+
+
+def add_tanh_norm(x: torch.Tensor, delta, alpha: float, weight: torch.Tensor, bias: torch.Tensor, out: torch.Tensor, rows=None) -> None:
+    """x += delta (when given; float32, in place), out = tanh(alpha x) * weight + bias in out's dtype. `delta`: a tensor in
+    out's dtype, a SplitSum, or a ScaledSum of up to two of those. With `rows` (int32 [R]) out[i] comes from row rows[i]
+    and x is left as it is."""
+    terms = delta.terms if isinstance(delta, ScaledSum) else ([(delta, 1.0)] if delta is not None else [])
+    _dev(x, weight, bias, out, rows)
+    D, n = x.shape[-1], out.shape[0]
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "add_tanh_norm: x must be float32 contiguous")
+    _need(all(w.dtype == torch.float32 and w.numel() == D for w in (weight, bias)), "add_tanh_norm: weight and bias must be float32 [D]")
+    _need(out.shape[-1] == D and out.is_contiguous(), "add_tanh_norm: out must be [n, D] contiguous")
+    _need(rows is None and n == x.shape[0] or rows is not None and rows.dtype == torch.int32 and rows.numel() == n,
+          "add_tanh_norm: out must have x's rows, or rows must be int32 [n]")
+    args = []
+    for t, c in terms + [(None, 0.0)] * (2 - len(terms)):
+        if isinstance(t, SplitSum):
+            _need(t.M == x.shape[0] and t.N == D, "add_tanh_norm: partial sums do not match x")
+            args += [0, t.partial.data_ptr(), t.stride, t.splits, c]
+        else:
+            if t is not None:
+                _dev(t)
+                _need(t.dtype == out.dtype and t.shape == x.shape and t.is_contiguous(), "add_tanh_norm: a delta must match x's shape and out's dtype")
+            args += [_ptr(t), 0, 0, 0, c]
+    call("tie_add_tanh_norm", dtype_code(out), x.data_ptr(), *args, _ptr(rows), float(alpha), weight.data_ptr(), bias.data_ptr(),
+         out.data_ptr(), n, D, _stream())
+
+
+def sinusoid_add(x: torch.Tensor, positions: torch.Tensor, base: float = 10000.0) -> None:
+    """x[t, 2i] += sin(p * base^(-2i/D)), x[t, 2i+1] += cos of the same angle, p = positions[t]; x float32 [T, D]."""
+    _dev(x, positions)
+    _need(x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2, "sinusoid_add: x must be float32 [T, D] contiguous")
+    _need(positions.dtype == torch.int32 and positions.numel() >= x.shape[0], "sinusoid_add: positions must be int32 [T]")
+    call("tie_sinusoid_add", x.data_ptr(), positions.data_ptr(), x.shape[0], x.shape[1], float(base), _stream())
+
+
+def two_branch_unit(z: torch.Tensor, out: torch.Tensor, c_pos: float, c_neg: float) -> None:
+    """out = c_pos z^2 + z/2 where z > 0, else c_neg (exp(z) - 1 - z) + z/2; z and out alike, contiguous."""
+    _dev(z, out)
+    _need(z.shape == out.shape and z.dtype == out.dtype and z.is_contiguous() and out.is_contiguous(), "two_branch_unit: z and out alike, contiguous")
+    call("tie_two_branch_unit", dtype_code(z), z.data_ptr(), out.data_ptr(), z.numel(), float(c_pos), float(c_neg), _stream())
+
+
+# -- attention whose query heads read slices of wider key rows (csrc/attention_simt.cu, csrc/score_maps.cu)
+
+def slice_norm_append(proj, q_off: int, nq: int, k_off: int, nk: int, v_off: int, v_width: int, dim: int, wq, wk, eps: float,
+                      slots, k_cache, v_cache) -> None:
+    """Per token of `proj` [T, width]: the nq slices of `dim` from column q_off are divided by their root mean square and
+    multiplied by wq (float32 [dim]; None: left alone), in place; with planes given, the nk slices from k_off likewise with
+    wk on their way into the key plane [pages, heads, page, k_row] and the v_width columns from v_off into the value plane
+    [pages, heads, page, v_row] at slots[t] (negative: nothing is written)."""
+    _dev(proj, wq, wk, slots, k_cache, v_cache)
+    T = proj.shape[0]
+    _need(proj.dim() == 2 and proj.stride(1) == 1, "slice_norm_append: proj rows must be contiguous")
+    for w in (wq, wk):
+        _need(w is None or (w.dtype == torch.float32 and w.numel() == dim), "slice_norm_append: a norm weight must be float32 [dim]")
+    write = k_cache is not None
+    heads = k_row = v_row = page = 0
+    if write:
+        _need(k_cache.dim() == 4 and v_cache.dim() == 4 and k_cache.is_contiguous() and v_cache.is_contiguous() and
+              k_cache.shape[:3] == v_cache.shape[:3] and k_cache.dtype == proj.dtype and v_cache.dtype == proj.dtype,
+              "slice_norm_append: planes [pages, heads, page, size] in proj's dtype")
+        heads, page, k_row, v_row = k_cache.shape[1], k_cache.shape[2], k_cache.shape[3], v_cache.shape[3]
+        _need(slots.dtype == torch.int32 and slots.numel() >= T, "slice_norm_append: slots must be int32 [T]")
+    call("tie_slice_norm_append", dtype_code(proj), proj.data_ptr(), proj.stride(0), q_off, nq, k_off, nk, v_off, v_width, dim, _ptr(wq),
+         _ptr(wk), float(eps), _ptr(slots), _ptr(k_cache), _ptr(v_cache), T, heads, k_row, v_row, page, 1 if write else 0, _stream())
+
+
+def _maps_common(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, dim, sub_count):
+    _need(k_cache.dim() == 4 and v_cache.dim() == 4 and k_cache.is_contiguous() and v_cache.is_contiguous() and
+          k_cache.shape[:3] == v_cache.shape[:3] and k_cache.dtype == q.dtype and v_cache.dtype == q.dtype,
+          "attention maps: planes [pages, heads, page, size] in q's dtype")
+    kv_heads, v_dim = k_cache.shape[1], v_cache.shape[3]
+    _need(k_cache.shape[3] >= sub_count * dim, "attention maps: key rows too short for their slices")
+    _need(q.dim() == 2 and q.stride(1) == 1 and q.shape[1] >= q_heads * dim, "attention maps: q too narrow")
+    _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape == (q.shape[0], q_heads * v_dim),
+          "attention maps: out must be float32 [T, q_heads * value row]")
+    S = context_lens.numel()
+    _need(query_start.dtype == torch.int32 and query_start.numel() == S + 1 and context_lens.dtype == torch.int32 and
+          block_tables.dtype == torch.int32 and block_tables.dim() == 2 and block_tables.shape[0] == S and block_tables.is_contiguous(),
+          "attention maps: query_start int32 [S+1], context_lens int32 [S], block_tables int32 [S, blocks]")
+    return S, kv_heads, v_dim
+
+
+def attention_maps_rows(q, k_cache, v_cache, out, seq_of_row, query_start, context_lens, block_tables, rows: int, q_heads: int, dim: int,
+                        sub_div: int, sub_count: int, scale: float, window: int = 0, chunk: int = 0, softcap: float = 0.0, r1=None,
+                        r2=None) -> None:
+    """The first `rows` rows of q, each over all keys it sees. Query head h reads kv head h // (q_heads / cached heads) and, of
+    that key row, the `dim` elements from ((h // sub_div) % sub_count) * dim; its softmax weights meet the whole value row.
+    `chunk` > 0: a position sees its own chunk of that many positions only; `softcap` > 0: score <- cap tanh(score / cap);
+    r1, r2 (float32 [q_heads]): score -= r1 ln(1 + r2 distance). out float32 [T, q_heads * value row]."""
+    _dev(q, k_cache, v_cache, out, seq_of_row, query_start, context_lens, block_tables, r1, r2)
+    S, kv_heads, v_dim = _maps_common(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, dim, sub_count)
+    call("tie_attention_maps_rows", dtype_code(q), q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+         seq_of_row.data_ptr(), query_start.data_ptr(), context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1],
+         int(rows), S, q_heads, kv_heads, dim, k_cache.shape[3], int(sub_div), int(sub_count), v_dim, k_cache.shape[2], int(window),
+         int(chunk), float(scale), float(softcap), _ptr(r1), _ptr(r2), _stream())
+
+
+def attention_maps_split(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads: int, dim: int, sub_div: int,
+                         sub_count: int, scale: float, seq_list, n_list: int, split_keys: int, max_splits: int, scratch, window: int = 0,
+                         chunk: int = 0, softcap: float = 0.0, r1=None, r2=None) -> None:
+    """The same for the sequences of seq_list, which bring one row each, their keys cut into splits of split_keys; scratch holds
+    attention_split_scratch_floats(n_list, q_heads, value row, max_splits) floats."""
+    _dev(q, k_cache, v_cache, out, query_start, context_lens, block_tables, seq_list, scratch, r1, r2)
+    S, kv_heads, v_dim = _maps_common(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, dim, sub_count)
+    _need(scratch.dtype == torch.float32 and scratch.numel() >= attention_split_scratch_floats(n_list, q_heads, v_dim, max_splits),
+          "attention maps: scratch too small")
+    call("tie_attention_maps_split", dtype_code(q), q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+         query_start.data_ptr(), context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], S, q_heads, kv_heads, dim,
+         k_cache.shape[3], int(sub_div), int(sub_count), v_dim, k_cache.shape[2], int(window), int(chunk), float(scale), float(softcap),
+         _ptr(r1), _ptr(r2), seq_list.data_ptr(), n_list, split_keys, max_splits, scratch.data_ptr(), _stream())
+
+
+def diff_combine(a, gate, lam: float, mult: float, eps: float, out, heads: int, vdim: int) -> None:
+    """a float32 [T, heads * 2 * vdim] (two maps a head): o = a1 - lam a2; out = (o / rms(o)) * mult * sigmoid(gate) per head; gate
+    (None: no gate; rows may be strided) and out [T, heads * vdim] in the compute dtype."""
+    _dev(a, gate, out)
+    T = a.shape[0]
+    _need(a.dtype == torch.float32 and a.is_contiguous() and a.shape == (T, heads * 2 * vdim), "diff_combine: a must be float32 [T, heads * 2 * vdim]")
+    _need(out.is_contiguous() and out.shape == (T, heads * vdim), "diff_combine: out must be [T, heads * vdim] contiguous")
+    _need(gate is None or (gate.dim() == 2 and gate.stride(1) == 1 and gate.shape == out.shape and gate.dtype == out.dtype),
+          "diff_combine: gate must be [T, heads * vdim] in out's dtype")
+    call("tie_diff_combine", dtype_code(out), a.data_ptr(), _ptr(gate), gate.stride(0) if gate is not None else 0, float(lam), float(mult),
+         float(eps), out.data_ptr(), T, heads, vdim, _stream())
+
+
+def head_talk(a, talk, out, heads: int, kv_heads: int, vdim: int) -> None:
+    """a float32 [T, heads * kv_heads * vdim] (every head's weights on every kv head's values): out[t, h] = sum_g talk[h, g] *
+    a[t, g, kv head of h]; talk float32 [heads, heads]; out [T, heads * vdim] in the compute dtype."""
+    _dev(a, talk, out)
+    T = a.shape[0]
+    _need(a.dtype == torch.float32 and a.is_contiguous() and a.shape == (T, heads * kv_heads * vdim), "head_talk: a must be float32 [T, heads * kv_heads * vdim]")
+    _need(talk.dtype == torch.float32 and talk.is_contiguous() and talk.shape == (heads, heads), "head_talk: talk must be float32 [heads, heads]")
+    _need(out.is_contiguous() and out.shape == (T, heads * vdim), "head_talk: out must be [T, heads * vdim] contiguous")
+    call("tie_head_talk", dtype_code(out), a.data_ptr(), talk.data_ptr(), out.data_ptr(), T, heads, kv_heads, vdim, _stream())
+
+
+# -- a recurrence that blends its inputs with the token before (csrc/time_mix.cu, csrc/delta_rule.cu)
+
+def token_shift_mix(h, mu, state, prev_off: int, ctx, out) -> None:
+    """out[t, m * D:(m + 1) * D] = h[t] + (h[t - 1] - h[t]) * mu[m]; the row before a portion's first row comes from the sequence's
+    row of `state` (float32 [slots, floats], at prev_off; zeros at position 0). h [T, D] and out [T, n * D] in the compute dtype, mu float32 [n, D]."""
+    _dev(h, mu, state, out)
+    T, D = h.shape
+    n = mu.shape[0]
+    _need(h.is_contiguous() and out.dtype == h.dtype and out.stride(1) == 1 and out.shape == (T, n * D), "token_shift_mix: out must be [T, n * D] in h's dtype")
+    _need(mu.dtype == torch.float32 and mu.is_contiguous() and mu.shape == (n, D), "token_shift_mix: mu must be float32 [n, D]")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1 and state.shape[1] >= prev_off + D, "token_shift_mix: state rows too short")
+    call("tie_token_shift_mix", dtype_code(h), h.data_ptr(), mu.data_ptr(), n, state.data_ptr(), state.stride(0), prev_off,
+         ctx.seq_of_row.data_ptr(), ctx.query_start.data_ptr(), ctx.positions.data_ptr(), ctx.state_slots.data_ptr(), out.data_ptr(),
+         out.stride(0), T, D, _stream())
+
+
+def tanh_rows(x, out) -> None:
+    """out[:, :cols] = tanh(x) (x float32 [T, cols], rows may be strided; out in the compute dtype, at least as wide)."""
+    _dev(x, out)
+    _need(x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1 and out.dim() == 2 and out.stride(1) == 1 and
+          out.shape[0] == x.shape[0] and out.shape[1] >= x.shape[1], "tanh_rows: x float32 [T, cols], out [T, >= cols]")
+    call("tie_tanh_rows", dtype_code(out), x.data_ptr(), x.stride(0), out.data_ptr(), out.stride(0), x.shape[0], x.shape[1], _stream())
+
+
+def time_mix_prep(r, k, v, w0, rn, kn, vn, decay) -> None:
+    """r, k, v [T, n] (compute dtype, one row stride) as float32 rows rn, kn, vn; decay (float32 [T, n], holding the raw
+    projection) <- exp(-exp(decay + w0)), w0 float32 [n]."""
+    _dev(r, k, v, w0, rn, kn, vn, decay)
+    T, n = decay.shape
+    _need(all(t.shape == (T, n) and t.stride(1) == 1 and t.stride(0) == r.stride(0) and t.dtype == r.dtype for t in (r, k, v)),
+          "time_mix_prep: r, k, v must be [T, n] alike")
+    _need(all(t.dtype == torch.float32 and t.is_contiguous() and t.shape == (T, n) for t in (rn, kn, vn, decay)) and
+          w0.dtype == torch.float32 and w0.numel() == n, "time_mix_prep: float32 [T, n] outputs, w0 float32 [n]")
+    call("tie_time_mix_prep", dtype_code(r), r.data_ptr(), k.data_ptr(), v.data_ptr(), r.stride(0), w0.data_ptr(), rn.data_ptr(),
+         kn.data_ptr(), vn.data_ptr(), decay.data_ptr(), T, n, _stream())
+
+
+def delta_rule_bonus(qn, kn, vn, decay, bonus, state, ctx, heads: int, dim: int, out) -> None:
+    """The plain recurrence read before it is written: per head o_t = (S + diag(bonus) k_t v_t^T)^T q_t, then
+    S <- diag(decay_t) S + k_t v_t^T. qn, kn, vn, decay, out float32 [T, heads * dim]; bonus float32 [heads * dim]; S [heads, dim, dim]
+    sits at the start of the sequence's row of `state`."""
+    _dev(qn, kn, vn, decay, bonus, state, out)
+    T = qn.shape[0]
+    _need(all(t.dtype == torch.float32 and t.is_contiguous() and t.shape == (T, heads * dim) for t in (qn, kn, vn, decay, out)),
+          "delta_rule_bonus: float32 [T, heads * dim] rows")
+    _need(bonus.dtype == torch.float32 and bonus.is_contiguous() and bonus.numel() == heads * dim, "delta_rule_bonus: bonus must be float32 [heads * dim]")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1 and state.shape[1] >= heads * dim * dim,
+          "delta_rule_bonus: state rows too short")
+    call("tie_delta_rule_bonus", F32, qn.data_ptr(), kn.data_ptr(), vn.data_ptr(), 0, decay.data_ptr(), decay.stride(0), state.data_ptr(),
+         state.stride(0), heads * dim * dim, qn.data_ptr(), qn.stride(0), 0, 0, 0, ctx.query_start.data_ptr(), ctx.state_slots.data_ptr(),
+         ctx.S, heads, heads, dim, dim, 1, out.data_ptr(), bonus.data_ptr(), _stream())
+
+
+def time_mix_out(o, gate, weight, eps: float, out, heads: int, dim: int, h, state, prev_off: int, ctx) -> None:
+    """out[t, hd] = (o[t, hd] / rms(o[t, hd])) * weight[hd] * silu(gate[t, hd]) per head of dim (weight float32 [heads * dim]); and the
+    last row of h of every sequence becomes the row its slot keeps (state[slot, prev_off:prev_off + D], float32)."""
+    _dev(o, gate, weight, out, h, state)
+    T, D = h.shape
+    _need(o.dtype == torch.float32 and o.is_contiguous() and o.shape == (T, heads * dim), "time_mix_out: o must be float32 [T, heads * dim]")
+    _need(gate.dim() == 2 and gate.stride(1) == 1 and gate.shape == o.shape and gate.dtype == out.dtype and out.is_contiguous() and
+          out.shape == o.shape, "time_mix_out: gate and out [T, heads * dim] in the compute dtype")
+    _need(weight.dtype == torch.float32 and weight.numel() == heads * dim and h.is_contiguous() and h.dtype == out.dtype,
+          "time_mix_out: weight float32 [heads * dim], h contiguous in the compute dtype")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1 and state.shape[1] >= prev_off + D, "time_mix_out: state rows too short")
+    call("tie_time_mix_out", dtype_code(out), o.data_ptr(), gate.data_ptr(), gate.stride(0), weight.data_ptr(), float(eps), out.data_ptr(), T,
+         heads, dim, h.data_ptr(), D, state.data_ptr(), state.stride(0), prev_off, ctx.seq_of_row.data_ptr(), ctx.query_start.data_ptr(),
+         ctx.state_slots.data_ptr(), _stream())

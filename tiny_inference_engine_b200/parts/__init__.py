@@ -3,7 +3,8 @@ from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSI
                    Embedding, FeedForward, Mixer, Norm, OutputHead, Part, PositionEncoding, StateNeed, StreamInput, build_part,
                    register_part, to_compute)
 from . import (norm, position, attention, gated_attention, delta, feed_forward, block, embedding,  # noqa: F401  (register the built-in kinds)
-               latent_attention, linear_attention, state_space, experts, stream_input, head_mix_attention)
+               latent_attention, linear_attention, state_space, experts, stream_input, head_mix_attention,
+               score_map_attention, time_mix)
 from .attention import GQAttention
 from .block import PreNormBlock
 from .embedding import LMHead, TokenEmbedding

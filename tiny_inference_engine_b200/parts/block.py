@@ -44,10 +44,15 @@ class PreNormBlock(Block):
 
 
 def as_delta(delta, norm, ctx, name):
-    """A SplitSum stays one for norms that add the splits themselves (`takes_split_sum`), else it is added up first."""
+    """A SplitSum stays one for norms that add the splits themselves (`takes_split_sum`), else it is added up first;
+    likewise a ScaledSum (sublayer outputs with a factor each) for norms that say `takes_scaled_sum`."""
     from .. import ops
     if isinstance(delta, ops.SplitSum) and not getattr(norm, "takes_split_sum", False):
         return delta.materialize(ctx.ws.rows(name, delta.M, delta.N, ctx.ws_dtype))
+    if isinstance(delta, ops.ScaledSum) and not getattr(norm, "takes_scaled_sum", False):
+        first = delta.terms[0][0]
+        M, N = (first.M, first.N) if isinstance(first, ops.SplitSum) else first.shape
+        return delta.materialize(ctx.ws.rows(name, M, N, ctx.ws_dtype))
     return delta
 
 

@@ -88,6 +88,22 @@ class PairHashEmbedding(TokenEmbedding):
                           self.buckets, self.mul_prev, self.mul_cur)
 
 
+class SinusoidTokenEmbedding(TokenEmbedding):
+    """x[t] = table[id] + e(position): e[2i] = sin(p * base^(-2i/hidden)), e[2i+1] = cos of the same angle, positions counted
+    from 0 in each sequence. The sum is float32. params beside `TokenEmbedding`'s: `base` (10000 when absent)."""
+
+    def __init__(self, spec, dtype, prefix: str = ""):
+        super().__init__(spec, dtype, prefix)
+        self.base = float(spec.params.get("base", 10000.0))
+
+    def forward(self, tokens, x):
+        raise InvalidArgument("this embedding reads each token's position: it is called with the step (`forward_step`)")
+
+    def forward_step(self, ctx, x, state):
+        ops.embed(self.table, ctx.tokens, x)
+        ops.sinusoid_add(x, ctx.positions, self.base)
+
+
 class LMHead(OutputHead):
     def __init__(self, spec, dtype, embedding: TokenEmbedding | None = None, prefix: str = ""):
         self.name = spec["name"]
@@ -120,4 +136,5 @@ class LMHead(OutputHead):
 register_part("embedding", "token_embedding", TokenEmbedding, replace=True)
 register_part("embedding", "normed_token_embedding", NormedTokenEmbedding, replace=True)
 register_part("embedding", "pair_hash_embedding", PairHashEmbedding, replace=True)
+register_part("embedding", "sinusoid_token_embedding", SinusoidTokenEmbedding, replace=True)
 register_part("head", "lm_head", LMHead, replace=True)

@@ -5,9 +5,10 @@
     chosen = the `top` experts with the largest c among the experts of the `group_keep` best of `group_count` equal
              blocks of consecutive experts (a block's score is the sum of its `group_top` largest c, 1: its best
              member's; ties go to the lower index; experts of other blocks count as minus infinity)
-    weight = s[chosen] / (sum of s[chosen] + 1e-20), or s[chosen] as it is (`renorm` false)
+    weight = s[chosen] / (sum of s[chosen] + 1e-20), or s[chosen] as it is (`renorm` false), times `weight_scale`
     out    = sum over chosen of weight * expert(h)
     expert = down(g * sigmoid(slope * g) * (u + up_shift)),  g = min(gate(h), limit), u = clamp(up(h), -limit, limit)
+             (`limit` None: no clamps; with slope 1 and up_shift 0 that is silu(gate(h)) * up(h))
 
 The router's product writes float32; routing (softmax, groups, top-k, weights) is one float kernel. Tokens are then
 listed by expert on the device (nothing of a step's routing reaches the host, so decode steps stay captured graphs),
@@ -15,7 +16,7 @@ and two grouped products run over that list, the clamped unit between them. The 
 weight * result as float32 partial sums [top, tokens, hidden], which the block's next residual add sums in order:
 the weighted sum over experts happens in float32 in the residual add itself. What a token computes depends on its
 own experts only, never on what else is in the step. params: `hidden_size`, `intermediate_size`, `num_experts`, `top`,
-`group_count`, `group_keep`, `group_top`, `score`, `correction`, `renorm`, `limit`, `slope`, `up_shift`; tensors `<prefix>router` and `<prefix>e<i>.gate|up|down`.
+`group_count`, `group_keep`, `group_top`, `score`, `correction`, `renorm`, `weight_scale`, `limit`, `slope`, `up_shift`; tensors `<prefix>router` and `<prefix>e<i>.gate|up|down`.
 """
 from __future__ import annotations
 
@@ -39,7 +40,9 @@ class RoutedExperts(FeedForward):
         self.hidden, self.inter = int(p["hidden_size"]), int(p["intermediate_size"])
         self.experts, self.top = int(p["num_experts"]), int(p["top"])
         self.group_count, self.group_keep = int(p.get("group_count", 1)), int(p.get("group_keep", 1))
-        self.limit, self.slope, self.up_shift = float(p["limit"]), float(p.get("slope", 1.0)), float(p.get("up_shift", 0.0))
+        self.limit = float(p["limit"]) if p.get("limit") is not None else float("inf")
+        self.slope, self.up_shift = float(p.get("slope", 1.0)), float(p.get("up_shift", 0.0))
+        self.weight_scale = float(p.get("weight_scale", 1.0))
         score = p.get("score", "softmax")
         if score not in ("softmax", "sigmoid"):
             raise InvalidArgument(f"experts: a router scores by 'softmax' or 'sigmoid', got '{score}'")
@@ -100,7 +103,7 @@ class RoutedExperts(FeedForward):
         ids = ctx.ws.rows("moe.ids", T, top, torch.int32)
         weights = ctx.ws.rows("moe.weights", T, top, torch.float32)
         ops.moe_route(logits[:, :E], top, self.group_count, self.group_keep, ids, weights, score_fn=self.score_fn,
-                      correction=self.correction, group_top=self.group_top, renorm=self.renorm)
+                      correction=self.correction, group_top=self.group_top, renorm=self.renorm, weight_scale=self.weight_scale)
         pairs = T * top
         few = pairs <= 8 * E      # an expert has a few rows: a warp per output column streams its weights once
         if self.in_blocks:

@@ -147,6 +147,50 @@ class BiasedGLU(FeedForward):
         return self.down(act, out, lambda n: ctx.ws.flat("ffn.out.partial", n, torch.float32, self._partial_capacity))
 
 
+class TwoBranchMLP(FeedForward):
+    """One hidden layer without a gate: down(act(up(h))), with an activation in two branches that meet at zero with the
+    slope 1/2 and whose curvatures are learned, two numbers a layer (`<prefix>act` = [a_pos, a_neg]):
+
+        z > 0:  softplus(a_pos) z^2 + z / 2;      z <= 0:  (1/2 + softplus(a_neg)) (exp(z) - 1 - z) + z / 2
+
+    The two softplus are formed once, in float64, when the tensor is bound. params: `hidden_size`, `intermediate_size`, and
+    the tensors' names (`up`, `down`, `act`) after `prefix`."""
+    launches_only = False
+
+    def __init__(self, spec, dtype, prefix: str = ""):
+        p = spec.params
+        self.prefix = prefix + p.get("prefix", "")
+        self.hidden, self.inter = int(p["hidden_size"]), int(p["intermediate_size"])
+        self.names = tuple(self.prefix + p.get(k, k) for k in ("up", "down", "act"))
+        self.dtype = dtype
+        self._partial_capacity = None
+
+    def needs(self):
+        u, d, a = self.names
+        return {u: TensorNeed((self.inter, self.hidden)), d: TensorNeed((self.hidden, self.inter)), a: TensorNeed((2,), "norm")}
+
+    def bind(self, get):
+        u, d, a = self.names
+        self.up = ops.bound_gemm(to_compute(get(u), self.dtype).contiguous(), split_many=False)
+        self.down = ops.bound_gemm(to_compute(get(d), self.dtype).contiguous())
+        self.w_up, self.w_down = self.up.w, self.down.w
+        a_pos, a_neg = (float(v) for v in get(a).to(torch.float64).cpu().reshape(-1)[:2])
+        softplus = lambda v: float(torch.nn.functional.softplus(torch.tensor(v, dtype=torch.float64)))
+        self.c_pos, self.c_neg = softplus(a_pos), 0.5 + softplus(a_neg)
+
+    def forward(self, h, ctx):
+        T = h.shape[0]
+        z = ctx.ws.rows("ffn.gate_up", T, self.inter, self.dtype)
+        self.up(h, z)
+        act = ctx.ws.rows("ffn.act", T, self.inter, self.dtype)
+        ops.two_branch_unit(z, act, self.c_pos, self.c_neg)
+        out = ctx.ws.rows("ffn.out", T, self.hidden, self.dtype)
+        if self._partial_capacity is None:
+            self._partial_capacity = ops.partial_capacity(ctx.ws.max_rows, self.down.N, self.down.K)
+        return self.down(act, out, lambda n: ctx.ws.flat("ffn.out.partial", n, torch.float32, self._partial_capacity))
+
+
 register_part("feed_forward", "swiglu", SwiGLU, replace=True)
+register_part("feed_forward", "two_branch_mlp", TwoBranchMLP, replace=True)
 register_part("feed_forward", "biased_glu", BiasedGLU, replace=True)
 register_part("feed_forward", "clamped_glu", ClampedGLU, replace=True)

@@ -88,3 +88,42 @@ class GroupedRMSNorm(Norm):
 
 
 register_part("norm", "grouped_rmsnorm", GroupedRMSNorm, replace=True)
+
+
+class DynamicTanh(Norm):
+    """A norm without statistics: tanh(alpha * x) * weight + bias, element by element, with a learned scalar alpha
+    (`<name>.alpha`) and a bias vector (`<name>.b`) stored beside the weight. No mean, no variance, no eps. The residual
+    add ahead of it is fused in as for the other norms, and it adds sums of sublayer outputs with factors (`ops.ScaledSum`)
+    and the partial sums of split products itself, in float32."""
+    launches_only = False
+    takes_split_sum = True
+    takes_scaled_sum = True
+
+    def __init__(self, spec, dtype, prefix: str = ""):
+        self.name = prefix + spec["name"]
+        self.size = int(spec["size"])
+        self.dtype = dtype
+        self.weight = self.bias = None
+        self.alpha = 1.0
+
+    def needs(self):
+        return {self.name: TensorNeed((self.size,), "norm"), self.name + ".b": TensorNeed((self.size,), "norm"),
+                self.name + ".alpha": TensorNeed((), "norm")}
+
+    def bind(self, get):
+        self.weight = get(self.name).to(torch.float32).contiguous()
+        self.bias = get(self.name + ".b").to(torch.float32).contiguous()
+        self.alpha = float(get(self.name + ".alpha").to(torch.float32).reshape(-1)[0].item())
+
+    def add_norm(self, x, delta, out, rows=None):
+        if isinstance(delta, ops.NormedDelta):
+            raise NotImplementedError("a dynamic tanh takes a plain delta, partial sums or a scaled sum, not one that still has a norm to pass")
+        ops.add_tanh_norm(x, delta, self.alpha, self.weight, self.bias, out, rows)
+
+    def rows(self, x, out):
+        if x.dtype != torch.float32 or not x.is_contiguous():
+            raise NotImplementedError("a dynamic tanh over other views than contiguous float32 rows")
+        ops.add_tanh_norm(x, None, self.alpha, self.weight, self.bias, out)
+
+
+register_part("norm", "dynamic_tanh", DynamicTanh, replace=True)
