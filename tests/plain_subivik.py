@@ -302,8 +302,9 @@ def moe(ff=24, experts=6, top=2, scale=1.5):
 
 
 def attention_layer(heads=4, kv_heads=2, dim=16, vdim=24, chunk=24, diff=0.3, scale=None, kv_from=None, mlp="dense"):
-    mx = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "mask": {"size": chunk}, "diff": diff,
-          "scale": float(scale if scale is not None else dim ** -0.5)}
+    mx = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "diff": diff, "scale": float(scale if scale is not None else dim ** -0.5)}
+    if chunk:
+        mx["mask"] = {"size": chunk}
     if kv_from is not None:
         mx["kv_from"] = kv_from
     return {"type": "attention", "mixer": mx, "mlp": dense() if mlp == "dense" else mlp}

@@ -147,6 +147,16 @@ def subivik_spec(c: SubivikConfig) -> ModelSpec:
     def norm(name: str) -> PartSpec:
         return PartSpec("dynamic_tanh", {"name": name, "size": D})
 
+    def chunk_of(mx) -> int:
+        return int((mx.get("mask") or {}).get("size") or 0)
+
+    # the cache of a layer that others read is kept as far back as the longest chunk among its readers (all of it if one has none)
+    spans = {}
+    for i, layer in enumerate(c.layers):
+        if layer["type"] == "attention":
+            owner = layer["mixer"].get("kv_from", i)
+            owner = i if owner is None else owner
+            spans.setdefault(owner, []).append(chunk_of(layer["mixer"]))
     layers, run_order = [], []
     for i, layer in enumerate(c.layers):
         p, mx, kind = f"l{i}.", layer["mixer"], layer["type"]
@@ -154,7 +164,8 @@ def subivik_spec(c: SubivikConfig) -> ModelSpec:
             mixer = PartSpec("differential_attention", {
                 "prefix": p + "mix.", "hidden_size": D, "num_heads": mx["heads"], "num_kv_heads": mx["kv_heads"], "head_dim": mx["dim"],
                 "value_dim": mx["vdim"], "scale": float(mx["scale"]), "diff": float(mx["diff"]), "eps": c.eps,
-                "chunk": int((mx.get("mask") or {}).get("size") or 0), "output_gate": True, "own_kv": mx.get("kv_from") is None})
+                "chunk": chunk_of(mx), "output_gate": True, "own_kv": mx.get("kv_from") is None,
+                "cache_span": 0 if min(spans.get(i, [0])) == 0 else max(spans[i])})
             run_order.append(RunEntry(i, cache_of=mx.get("kv_from")))       # no layer runs twice: entry j is layer j
         else:
             lf, rt = mx["left"], mx["right"]

@@ -108,6 +108,8 @@ class DifferentialAttention(_SliceAttention):
         p = spec.params
         self._sizes(p, prefix)
         self.chunk = int(p.get("chunk") or 0)
+        # how far back the cache is read by this entry and by the entries that read its cache (0: all the way)
+        self.cache_span = int(p["cache_span"]) if p.get("cache_span") is not None else self.chunk
         self.diff = float(p["diff"])
         self.output_gate = bool(p.get("output_gate", True))
         self.own_kv = bool(p.get("own_kv", True))        # False: the entry reads another entry's cache
@@ -146,7 +148,7 @@ class DifferentialAttention(_SliceAttention):
 
     def cache_need(self):
         # a chunk never reaches further back than its own length: pages behind that go back like a window's
-        return CacheNeed("window" if self.chunk > 0 else "full", self.kv_heads, 2 * self.dim, self.chunk, value_dim=self.vdim)
+        return CacheNeed("window" if self.cache_span > 0 else "full", self.kv_heads, 2 * self.dim, self.cache_span, value_dim=self.vdim)
 
     def forward(self, h, ctx, cache, state):
         T, H = h.shape[0], self.heads
