@@ -219,6 +219,30 @@ def lufatar_config(width, layers, heads, kv_heads, ff, vocab, vdim=128):
             "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}}, "vocab": vocab, "width": width}
 
 
+def subivik_config(width, layers, heads, kv_heads, ff, vocab, chunk=1024, vdim=128):
+    """Differential attention in chunks and parallel layers (talking-heads attention beside a token-shift recurrence) in turn at
+    the sizes of a Qwen3 layer; every second attention layer reads the keys and values of the one before it; feed-forwards dense
+    and routed in turn, the routed one with as many active parameters as the dense one (4 of 32 experts of ff / 4). The left half
+    of a parallel layer has half of the heads over two kv heads, the right half as many heads of 64 as make up the width."""
+    dense = {"ff": ff, "kind": "dense"}
+    routed = {"expert": {"ff": ff // 4}, "kind": "moe", "router": {"experts": 32, "top": 4, "scale": 2.5}}
+    att = {"dim": 128, "heads": heads, "kv_heads": kv_heads, "vdim": vdim, "mask": {"size": chunk}, "scale": 128 ** -0.5, "diff": 0.6}
+    par = {"left": {"dim": 128, "heads": heads // 2, "kv_heads": 2, "vdim": vdim, "scale": 128 ** -0.5, "softcap": 50.0},
+           "right": {"dim": 64, "heads": width // 64}, "left_scale": 0.6, "right_scale": 0.9}
+    out, owner = [], None
+    for i in range(layers):
+        if i % 2 == 0:
+            mx = dict(att)
+            if owner is not None and (i // 2) % 2 == 1:
+                mx["kv_from"] = owner
+            else:
+                owner = i
+            out.append({"type": "attention", "mixer": mx, "mlp": dense if (i // 2) % 2 == 0 else routed})
+        else:
+            out.append({"type": "parallel", "mixer": par, "mlp": routed if (i // 2) % 2 == 0 else dense})
+    return {"architecture": "Subivik", "layers": out, "norm": {"eps": 1e-6}, "vocab": vocab, "width": width}
+
+
 DESIGN_SIZES = {     # name: (width, layers, heads, kv heads, feed-forward, vocab)
     "2048x16": (2048, 16, 16, 8, 6144, 151936),
     "4096x8": (4096, 8, 32, 8, 12288, 151936),
@@ -242,6 +266,8 @@ def design_bench(args) -> dict:
         if args.layers:
             layers = args.layers
         configs = {"misudra": misudra_config(width, layers * 2 // 3, heads, kv_heads, ff, vocab)} if args.design in ("misudra", "lufatar") else {}
+        if args.design == "subivik":
+            configs = {"subivik": subivik_config(width, layers, heads, kv_heads, ff, vocab, vdim=args.design_vdim)}
         if args.design == "lufatar":
             configs = {"lufatar": lufatar_config(width, layers * 2 // 3, heads, kv_heads, ff, vocab, vdim=args.design_vdim), **configs}
         configs.update({"dugazen": dugazen_config(width, layers, heads, kv_heads, ff, vocab, vdim=args.design_vdim),
@@ -348,11 +374,11 @@ def main() -> int:
     ap.add_argument("--profile", choices=["decode", "prefill", "mixed"], help="run two steps of one kind (mixed: 30 requests "
                     "decoding at context 2,048 beside a 482-token portion of a prompt, the serving default of 512 tokens a step), kernel by kernel, between "
                     "cudaProfilerStart/Stop (for ncu --profile-from-start off) and print no bench line")
-    ap.add_argument("--design", choices=["dugazen", "misudra", "lufatar"], help="prefill and decode throughput of that design beside Qwen3 at equal "
+    ap.add_argument("--design", choices=["dugazen", "misudra", "lufatar", "subivik"], help="prefill and decode throughput of that design beside Qwen3 at equal "
                     "sizes (a line of its own; the default workload and its line stay as they are)")
     ap.add_argument("--design-size", choices=sorted(DESIGN_SIZES), help="--design: one size only")
     ap.add_argument("--design-vdim", type=int, default=128, help="--design: size of a value head (keys have 128)")
-    ap.add_argument("--design-only", choices=["dugazen", "misudra", "lufatar", "qwen3"], help="--design: one of the two models only")
+    ap.add_argument("--design-only", choices=["dugazen", "misudra", "lufatar", "subivik", "qwen3"], help="--design: one of the two models only")
     args = ap.parse_args()
 
     if args.design:

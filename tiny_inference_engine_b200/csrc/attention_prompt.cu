@@ -32,7 +32,22 @@ struct PromptArgs {
   int max_blocks, q_heads, kv_heads, page_size, page_shift, window;
   float scale_log2;
   int exact_weights;      // != 0: the softmax weights enter the value product as two bfloat16 terms (pv_tile)
+  // Key and value slices of wider cached rows (all zero: every kv head a cached head, rows of DH). The planes hold
+  // `cache_heads` heads with key rows of k_ld and value rows of v_ld elements; kv head v of the launch reads cached head
+  // v % cache_heads, the DH key elements from (v / cache_heads) * DH and the DH value elements from
+  // ((v / cache_heads + v_shift) % (v_ld / DH)) * DH, and writes its output as slice number that of v_ld / DH slices a head.
+  int cache_heads, k_ld, v_ld, v_shift;
+  int chunk;              // > 0: a position sees the keys of its own chunk of this many positions (counted from 0) only
+  float softcap;          // > 0: score <- softcap * tanh(score / softcap), ahead of the bias
+  const float* r1;        // [q_heads] or null: score -= r1[h] * ln(1 + r2[h] * (position - key position))
+  const float* r2;
 };
+
+// The first key that position `pos` sees.
+__device__ __forceinline__ int prompt_first_visible(int pos, int window, int chunk) {
+  if (chunk > 0) return pos / chunk * chunk;
+  return window > 0 ? max(0, pos - window + 1) : 0;
+}
 
 template <int DH, int STAGES>
 __global__ void __launch_bounds__(kPromptThreads) attn_prompt_tma_kernel(const __grid_constant__ CUtensorMap k_map,
@@ -61,7 +76,13 @@ __global__ void __launch_bounds__(kPromptThreads) attn_prompt_tma_kernel(const _
   const int pos0 = a.context_lens[seq] - nq;                      // position of the sequence's first query of this step
   const int last_row = min(rows, row0 + 64) - 1;
   const int hi_cta = pos0 + last_row / G;
-  const int lo_cta = a.window > 0 ? max(0, pos0 + row0 / G - a.window + 1) : 0;
+  const bool limited = a.window > 0 || a.chunk > 0;               // rows do not see all earlier keys
+  const bool shaped = a.softcap > 0.0f || a.r1 != nullptr;        // scores pass a cap or a bias: no tile is taken whole
+  const int lo_cta = prompt_first_visible(pos0 + row0 / G, a.window, a.chunk);
+  const int cache_heads = a.cache_heads > 0 ? a.cache_heads : a.kv_heads;
+  const int cached_head = kvh % cache_heads, k_col = (kvh / cache_heads) * DH;
+  const int v_slices = a.v_ld > 0 ? a.v_ld / DH : 1;
+  const int v_slice = (kvh / cache_heads + a.v_shift) % v_slices, v_col = v_slice * DH;
   const int kt_first = lo_cta / kKeysPerTile, kt_last = hi_cta / kKeysPerTile;
   const int n_tiles = kt_last - kt_first + 1;
   const int box_rows = min(a.page_size, kKeysPerTile);
@@ -113,24 +134,28 @@ __global__ void __launch_bounds__(kPromptThreads) attn_prompt_tma_kernel(const _
         const int key = (kt_first + i) * kKeysPerTile + lane * box_rows;
         const int idx = key >> a.page_shift;
         const int page = idx < a.max_blocks ? table[idx] : 0;   // beyond the table: any real page; those keys are masked
-        const int row = (page * a.kv_heads + kvh) * a.page_size + (key & (a.page_size - 1));
+        const int row = (page * cache_heads + cached_head) * a.page_size + (key & (a.page_size - 1));
         uint8_t* kdst = smem + s * STAGE_BYTES + lane * box_rows * 128;
 #pragma unroll
         for (int h = 0; h < HALVES; ++h) {
-          tma_load_2d(kdst + h * (64 * 128), &k_map, h * 64, row, full + s);
-          tma_load_2d(kdst + PLANE_BYTES + h * (64 * 128), &v_map, h * 64, row, full + s);
+          tma_load_2d(kdst + h * (64 * 128), &k_map, k_col + h * 64, row, full + s);
+          tma_load_2d(kdst + PLANE_BYTES + h * (64 * 128), &v_map, v_col + h * 64, row, full + s);
         }
       }
     }
   } else {
     // ---- consumers: warp w owns rows row0 + 16 w .. + 15
     const int g = lane >> 2, tq = lane & 3;
-    int row_pos[2];
+    int row_pos[2], row_lo[2];
+    float row_r1[2] = {0.0f, 0.0f}, row_r2[2] = {0.0f, 0.0f};
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       const int row = row0 + warp * 16 + g + 8 * half;
       row_pos[half] = row < rows ? pos0 + row / G : -1;
+      row_lo[half] = row < rows ? prompt_first_visible(row_pos[half], a.window, a.chunk) : 0;
+      if (a.r1 != nullptr && row < rows) row_r1[half] = a.r1[kvh * G + row % G], row_r2[half] = a.r2[kvh * G + row % G];
     }
+    const float scale = a.scale_log2 * 0.6931471805599453f;
     const bool warp_has_rows = row0 + warp * 16 < rows;
     const int warp_hi = warp_has_rows ? pos0 + min(rows - 1, row0 + warp * 16 + 15) / G : -1;   // largest position of the warp's rows
     const int warp_lo = warp_has_rows ? pos0 + (row0 + warp * 16) / G : -1;                     // smallest
@@ -143,7 +168,7 @@ __global__ void __launch_bounds__(kPromptThreads) attn_prompt_tma_kernel(const _
       const int s = i % STAGES;
       if (!mbar_wait(full + s, (i / STAGES) & 1, abort_flag, a.status, 12)) break;
       const int key0 = (kt_first + i) * kKeysPerTile;
-      const bool in_window = a.window <= 0 || key0 + 63 > warp_lo - a.window;   // some key of the tile is inside some row's window
+      const bool in_window = !limited || key0 + 63 >= prompt_first_visible(warp_lo, a.window, a.chunk);   // some key of the tile is seen by some row
       if (key0 <= warp_hi && in_window) {
         const uint32_t k_tile = smem_u32(smem + s * STAGE_BYTES);
         float sc[8][4];
@@ -151,7 +176,8 @@ __global__ void __launch_bounds__(kPromptThreads) attn_prompt_tma_kernel(const _
         for (int j = 0; j < 8; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.0f;
         qk_tile<DH, 8, L>(sc, qf, k_tile, 0);
         // no mask where every key of the tile is at or below every row's position and inside every row's window
-        const bool full_tile = row0 + warp * 16 + 15 < rows && key0 + 63 <= warp_lo && (a.window <= 0 || key0 > warp_hi - a.window);
+        const bool full_tile = !shaped && row0 + warp * 16 + 15 < rows && key0 + 63 <= warp_lo &&
+                               (!limited || key0 >= prompt_first_visible(warp_hi, a.window, a.chunk));
         if (full_tile) {
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
@@ -165,8 +191,15 @@ __global__ void __launch_bounds__(kPromptThreads) attn_prompt_tma_kernel(const _
             for (int e = 0; e < 4; ++e) {
               const int key = key0 + j * 8 + tq * 2 + (e & 1);
               const int pos = row_pos[e >> 1];
-              const bool ok = key <= pos && (a.window <= 0 || key > pos - a.window);
-              sc[j][e] = ok ? sc[j][e] * a.scale_log2 : -INFINITY;
+              const bool ok = key <= pos && key >= row_lo[e >> 1];
+              float v = sc[j][e] * a.scale_log2;
+              if (shaped && ok) {
+                v = sc[j][e] * scale;
+                if (a.softcap > 0.0f) v = a.softcap * tanhf(v / a.softcap);
+                if (a.r1 != nullptr) v -= row_r1[e >> 1] * log1pf(row_r2[e >> 1] * static_cast<float>(pos - key));
+                v *= 1.4426950408889634f;
+              }
+              sc[j][e] = ok ? v : -INFINITY;
             }
           }
         }
@@ -182,7 +215,7 @@ __global__ void __launch_bounds__(kPromptThreads) attn_prompt_tma_kernel(const _
       const int row = row0 + warp * 16 + g + 8 * half;
       if (row >= rows) continue;
       const float inv = l[half] > 0.0f ? 1.0f / l[half] : 0.0f;
-      __nv_bfloat16* o = a.out + (static_cast<long long>(t0 + row / G) * a.q_heads + kvh * G + row % G) * DH;
+      __nv_bfloat16* o = a.out + ((static_cast<long long>(t0 + row / G) * a.q_heads + kvh * G + row % G) * v_slices + v_slice) * DH;
 #pragma unroll
       for (int j = 0; j < DH / 8; ++j) {
         *reinterpret_cast<uint32_t*>(o + j * 8 + tq * 2) = pack_bf16(acc[j][2 * half] * inv, acc[j][2 * half + 1] * inv);
@@ -225,7 +258,8 @@ using namespace tie;
 static int prompt_tma(const void* q, long long q_stride, const void* k_cache, const void* v_cache, void* out,
                       const int* query_start, const int* context_lens, const int* block_tables, int max_blocks, int n_seqs,
                       int max_queries, int q_heads, int kv_heads, int head_dim, int page_size, int pages, int window,
-                      float scale, int exact_weights, cudaStream_t s) {
+                      float scale, int exact_weights, cudaStream_t s, int cache_heads = 0, int k_ld = 0, int v_ld = 0, int v_shift = 0,
+                      int chunk = 0, float softcap = 0.0f, const float* r1 = nullptr, const float* r2 = nullptr) {
   TIE_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256, "attention_prompt: head_dim %d is not 64, 128 or 256", head_dim);
   TIE_REQUIRE(q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0 && q_heads / kv_heads <= 16,
               "attention_prompt: %d query heads over %d kv heads (at most 16 per group)", q_heads, kv_heads);
@@ -237,14 +271,20 @@ static int prompt_tma(const void* q, long long q_stride, const void* k_cache, co
   while ((1 << shift) < page_size) ++shift;
   const int box_rows = page_size < kKeysPerTile ? page_size : kKeysPerTile;
   CUtensorMap km, vm;
-  const long long rows = static_cast<long long>(pages) * kv_heads * page_size;
-  TIE_REQUIRE(make_map_bf16(&km, k_cache, rows, head_dim, head_dim, 64, box_rows) &&
-                  make_map_bf16(&vm, v_cache, rows, head_dim, head_dim, 64, box_rows),
+  const int heads_cached = cache_heads > 0 ? cache_heads : kv_heads;
+  const int k_row = k_ld > 0 ? k_ld : head_dim, v_row = v_ld > 0 ? v_ld : head_dim;
+  TIE_REQUIRE(kv_heads % heads_cached == 0 && k_row % 8 == 0 && v_row % head_dim == 0 && k_row >= (kv_heads / heads_cached) * head_dim &&
+                  chunk >= 0 && v_shift >= 0 && (r1 == nullptr) == (r2 == nullptr),
+              "attention_prompt: %d kv heads as slices of %d cached heads with key rows of %d and value rows of %d: impossible", kv_heads,
+              heads_cached, k_row, v_row);
+  const long long rows = static_cast<long long>(pages) * heads_cached * page_size;
+  TIE_REQUIRE(make_map_bf16(&km, k_cache, rows, k_row, k_row, 64, box_rows) &&
+                  make_map_bf16(&vm, v_cache, rows, v_row, v_row, 64, box_rows),
               "attention_prompt: cuTensorMapEncodeTiled failed");
   TIE_REQUIRE(status_word() != nullptr, "attention_prompt: cannot allocate the status word");
   PromptArgs a{static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out), query_start, context_lens, block_tables,
                status_word(), q_stride, max_blocks, q_heads, kv_heads, page_size, shift, window, scale * 1.4426950408889634f,
-               exact_weights};
+               exact_weights, cache_heads, k_ld, v_ld, v_shift, chunk, softcap, r1, r2};
   const int max_rows = max_queries * (q_heads / kv_heads);
   int st = kOk;
   if (head_dim == 64) st = launch_prompt_tma<64>(km, vm, a, n_seqs, max_rows, s);
@@ -269,4 +309,19 @@ TIE_API int tie_attention_prompt_tma_exact(const void* q, long long q_stride, co
                                            int head_dim, int page_size, int pages, int window, float scale, cudaStream_t s) {
   return prompt_tma(q, q_stride, k_cache, v_cache, out, query_start, context_lens, block_tables, max_blocks, n_seqs, max_queries,
                     q_heads, kv_heads, head_dim, page_size, pages, window, scale, 1, s);
+}
+
+// Score maps over slices of wider cached rows (the fields of PromptArgs behind exact_weights), with the softmax weights kept
+// to 16 bits of mantissa: kv head v of the launch reads cached head v % cache_heads, its DH key elements at column
+// (v / cache_heads) * DH of key rows of k_ld and its DH value elements at column ((v / cache_heads + v_shift) % (v_ld / DH)) * DH
+// of value rows of v_ld; out is [T, q_heads, v_ld / DH, DH] and the launch fills the slice of its value column. Chunks, a cap on
+// the scores and a bias by the logarithm of the distance are options.
+TIE_API int tie_attention_prompt_maps(const void* q, long long q_stride, const void* k_cache, const void* v_cache, void* out,
+                                      const int* query_start, const int* context_lens, const int* block_tables, int max_blocks,
+                                      int n_seqs, int max_queries, int q_heads, int kv_heads, int head_dim, int page_size, int pages,
+                                      int window, float scale, int cache_heads, int k_ld, int v_ld, int v_shift, int chunk,
+                                      float softcap, const float* r1, const float* r2, cudaStream_t s) {
+  return prompt_tma(q, q_stride, k_cache, v_cache, out, query_start, context_lens, block_tables, max_blocks, n_seqs, max_queries,
+                    q_heads, kv_heads, head_dim, page_size, pages, window, scale, 1, s, cache_heads, k_ld, v_ld, v_shift, chunk, softcap,
+                    r1, r2);
 }

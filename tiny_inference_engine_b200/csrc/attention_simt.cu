@@ -52,6 +52,7 @@ struct AttnArgs {
   const float* r1;          // [q_heads] or null: score -= r1[h] * ln(1 + r2[h] * (position - key position))
   const float* r2;
   int out_f32;              // the output rows are float whatever the storage type
+  int group;                // > 0: query head h reads cached head (h / group) % kv_heads (query heads laid out map by map)
 };
 
 // The first key that position `pos` sees.
@@ -124,6 +125,10 @@ __device__ __forceinline__ void attend_range(const float* __restrict__ qs, const
   }
 }
 
+__device__ __forceinline__ int kv_head_of(const AttnArgs& a, int h) {
+  return a.group > 0 ? (h / a.group) % a.kv_heads : h / (a.q_heads / a.kv_heads);
+}
+
 __device__ __forceinline__ int key_offset(const AttnArgs& a, int h) {
   return a.sub_count > 1 ? ((h / a.sub_div) % a.sub_count) * a.head_dim : 0;
 }
@@ -145,7 +150,7 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(AttnArgs a) {
   const int qs0 = a.query_start[s], qs1 = a.query_start[s + 1];
   const int pos = a.context_lens[s] - (qs1 - qs0) + (t - qs0);
   const int lo = first_visible(pos, a.window, a.chunk);
-  const int kvh = h / (a.q_heads / a.kv_heads);
+  const int kvh = kv_head_of(a, h);
 
   float* qs = smem + warp * a.head_dim;
   const T* qv = static_cast<const T*>(a.q) + static_cast<long long>(t) * a.q_stride + static_cast<long long>(h) * a.head_dim;
@@ -192,7 +197,7 @@ __global__ void __launch_bounds__(128) attention_split_kernel(AttnArgs a, const 
   // The last split takes whatever is left, so that a context longer than max_splits * split_keys (a caller
   // who sized max_splits from something else than the longest context) costs time, never keys.
   const int hi = split == max_splits - 1 ? pos : min(pos, lo + split_keys - 1);
-  const int kvh = h / (a.q_heads / a.kv_heads);
+  const int kvh = kv_head_of(a, h);
 
   float* qs = smem + warp * a.head_dim;
   const T* qv = static_cast<const T*>(a.q) + static_cast<long long>(t) * a.q_stride + static_cast<long long>(h) * a.head_dim;
@@ -425,17 +430,19 @@ TIE_API int tie_attention_split_dv(int dtype, const void* q, long long q_stride,
 
 // Score maps over slices of wider key rows (the fields of AttnArgs behind v_ld): the planes are
 // [pages, kv_heads, page_size, k_ld] and [pages, kv_heads, page_size, v_dim]; query head h reads kv head
-// h / (q_heads / kv_heads) and, of its key row, the head_dim elements from ((h / sub_div) % sub_count) * head_dim;
+// (h / group) % kv_heads and, of its key row, the head_dim elements from ((h / sub_div) % sub_count) * head_dim;
 // its softmax weights meet the whole value row. Chunks, a cap on the scores and a bias by the logarithm of the
 // distance are options. The output rows [T, q_heads * v_dim] are float.
 TIE_API int tie_attention_maps_rows(int dtype, const void* q, long long q_stride, const void* k_cache, const void* v_cache,
                                     float* out, const int* seq_of_row, const int* query_start, const int* context_lens,
                                     const int* block_tables, int max_blocks, int rows, int seqs, int q_heads, int kv_heads,
                                     int head_dim, int k_ld, int sub_div, int sub_count, int v_dim, int page_size, int window,
-                                    int chunk, float scale, float softcap, const float* r1, const float* r2, cudaStream_t s) {
+                                    int chunk, float scale, float softcap, const float* r1, const float* r2, int group,
+                                    cudaStream_t s) {
   const AttnArgs a{q, k_cache, v_cache, out, seq_of_row, query_start, context_lens, block_tables, q_stride, max_blocks,
                    rows, seqs, q_heads, kv_heads, head_dim, page_size, window, scale, v_dim, 0, k_ld, sub_div, sub_count,
-                   chunk, softcap, r1, r2, 1};
+                   chunk, softcap, r1, r2, 1, group};
+  TIE_REQUIRE(group > 0, "attention maps: query heads per cached head must be positive");
   TIE_REQUIRE(sub_div > 0 && sub_count > 0 && k_ld >= sub_count * head_dim && chunk >= 0 && (r1 == nullptr) == (r2 == nullptr),
               "attention maps: %d slices of %d do not fit key rows of %d", sub_count, head_dim, k_ld);
   if (const int st = check_attn(a, true)) return st;
@@ -449,11 +456,12 @@ TIE_API int tie_attention_maps_split(int dtype, const void* q, long long q_strid
                                      float* out, const int* query_start, const int* context_lens, const int* block_tables,
                                      int max_blocks, int seqs, int q_heads, int kv_heads, int head_dim, int k_ld, int sub_div,
                                      int sub_count, int v_dim, int page_size, int window, int chunk, float scale, float softcap,
-                                     const float* r1, const float* r2, const int* seq_list, int n_list, int split_keys,
+                                     const float* r1, const float* r2, int group, const int* seq_list, int n_list, int split_keys,
                                      int max_splits, float* scratch, cudaStream_t s) {
   const AttnArgs a{q, k_cache, v_cache, out, nullptr, query_start, context_lens, block_tables, q_stride, max_blocks,
                    0, seqs, q_heads, kv_heads, head_dim, page_size, window, scale, v_dim, 0, k_ld, sub_div, sub_count,
-                   chunk, softcap, r1, r2, 1};
+                   chunk, softcap, r1, r2, 1, group};
+  TIE_REQUIRE(group > 0, "attention maps: query heads per cached head must be positive");
   TIE_REQUIRE(sub_div > 0 && sub_count > 0 && k_ld >= sub_count * head_dim && chunk >= 0 && (r1 == nullptr) == (r2 == nullptr),
               "attention maps: %d slices of %d do not fit key rows of %d", sub_count, head_dim, k_ld);
   if (const int st = check_attn(a, true)) return st;

@@ -6,9 +6,9 @@
 //                       multiplied by a weight shared by all slices (in place; skipped without a weight), every slice
 //                       of the k columns likewise on its way into the key plane, the v columns copied into the value
 //                       plane. Key rows hold `k_row` elements per cached head, value rows `v_row`.
-//   diff_combine        two maps a head, a [T, H, 2, vdim] float: o = a1 - lambda a2, o / rms(o) * mult, times
-//                       sigmoid(gate), into the compute type.
-//   head_talk           a [T, H, G, vdim] float (every head's weights on every kv head's values):
+//   diff_combine        two maps a head, a [T, 2, H, vdim] (float, or the compute type): o = a1 - lambda a2,
+//                       o / rms(o) * mult, times sigmoid(gate), into the compute type.
+//   head_talk           a [T, H, G, vdim] (float, or the compute type; every head's weights on every kv head's values):
 //                       out[t, h] = sum_g talk[h, g] a[t, g, kv head of h], into the compute type.
 #include <math.h>
 
@@ -64,8 +64,8 @@ __global__ void __launch_bounds__(128) slice_norm_append_kernel(T* __restrict__ 
   }
 }
 
-template <typename T>
-__global__ void __launch_bounds__(128) diff_combine_kernel(const float* __restrict__ a, const T* __restrict__ gate,
+template <typename T, typename A>
+__global__ void __launch_bounds__(128) diff_combine_kernel(const A* __restrict__ a, const T* __restrict__ gate,
                                                            long long gate_stride, float lambda, float mult, float eps,
                                                            T* __restrict__ out, int heads, int vdim, long long items) {
   pdl_sync();
@@ -74,35 +74,35 @@ __global__ void __launch_bounds__(128) diff_combine_kernel(const float* __restri
   if (item >= items) return;
   const long long t = item / heads;
   const int h = static_cast<int>(item % heads);
-  const float* a1 = a + item * 2 * vdim;
-  const float* a2 = a1 + vdim;
+  const A* a1 = a + (t * 2 * heads + h) * vdim;
+  const A* a2 = a1 + static_cast<long long>(heads) * vdim;
   float ss = 0.0f;
   for (int d = lane; d < vdim; d += 32) {
-    const float o = a1[d] - lambda * a2[d];
+    const float o = ld(a1 + d) - lambda * ld(a2 + d);
     ss = fmaf(o, o, ss);
   }
   ss = warp_sum(ss);
   const float inv = 1.0f / sqrtf(ss / static_cast<float>(vdim) + eps);
   for (int d = lane; d < vdim; d += 32) {
-    const float o = a1[d] - lambda * a2[d];
+    const float o = ld(a1 + d) - lambda * ld(a2 + d);
     float v = (o * inv) * mult;
     if (gate != nullptr) v *= 1.0f / (1.0f + expf(-ld(gate + t * gate_stride + h * vdim + d)));
     st(out + item * vdim + d, v);
   }
 }
 
-template <typename T>
-__global__ void __launch_bounds__(256) head_talk_kernel(const float* __restrict__ a, const float* __restrict__ talk,
+template <typename T, typename A>
+__global__ void __launch_bounds__(256) head_talk_kernel(const A* __restrict__ a, const float* __restrict__ talk,
                                                         T* __restrict__ out, int heads, int kv_heads, int vdim) {
   pdl_sync();
   const long long t = blockIdx.x;
   const int per = heads / kv_heads;
-  const float* row = a + t * heads * kv_heads * vdim;
+  const A* row = a + t * heads * kv_heads * vdim;
   for (int i = threadIdx.x; i < heads * vdim; i += blockDim.x) {
     const int h = i / vdim, d = i % vdim;
     const int c = h / per;
     float acc = 0.0f;
-    for (int g = 0; g < heads; ++g) acc = fmaf(talk[h * heads + g], row[(g * kv_heads + c) * vdim + d], acc);
+    for (int g = 0; g < heads; ++g) acc = fmaf(talk[h * heads + g], ld(row + (g * kv_heads + c) * vdim + d), acc);
     st(out + t * heads * vdim + i, acc);
   }
 }
@@ -137,17 +137,20 @@ TIE_API int tie_slice_norm_append(int dtype, void* proj, long long stride, int q
   TIE_RETURN_LAUNCH("slice_norm_append");
 }
 
-TIE_API int tie_diff_combine(int dtype, const float* a, const void* gate, long long gate_stride, float lambda, float mult,
+TIE_API int tie_diff_combine(int dtype, int a_f32, const void* a, const void* gate, long long gate_stride, float lambda, float mult,
                              float eps, void* out, int tokens, int heads, int vdim, cudaStream_t s) {
   TIE_REQUIRE(tokens >= 0 && heads > 0 && vdim > 0, "diff_combine: bad sizes tokens=%d heads=%d vdim=%d", tokens, heads, vdim);
   const long long items = static_cast<long long>(tokens) * heads;
   if (items == 0) return kOk;
   if (dtype == TIE_F32) {
-    TIE_LAUNCH((diff_combine_kernel<float>), ceil_div(items, 4), 128, 0, s, a, static_cast<const float*>(gate), gate_stride, lambda,
-               mult, eps, static_cast<float*>(out), heads, vdim, items);
+    TIE_LAUNCH((diff_combine_kernel<float, float>), ceil_div(items, 4), 128, 0, s, static_cast<const float*>(a), static_cast<const float*>(gate),
+               gate_stride, lambda, mult, eps, static_cast<float*>(out), heads, vdim, items);
+  } else if (dtype == TIE_BF16 && a_f32) {
+    TIE_LAUNCH((diff_combine_kernel<__nv_bfloat16, float>), ceil_div(items, 4), 128, 0, s, static_cast<const float*>(a),
+               static_cast<const __nv_bfloat16*>(gate), gate_stride, lambda, mult, eps, static_cast<__nv_bfloat16*>(out), heads, vdim, items);
   } else if (dtype == TIE_BF16) {
-    TIE_LAUNCH((diff_combine_kernel<__nv_bfloat16>), ceil_div(items, 4), 128, 0, s, a, static_cast<const __nv_bfloat16*>(gate),
-               gate_stride, lambda, mult, eps, static_cast<__nv_bfloat16*>(out), heads, vdim, items);
+    TIE_LAUNCH((diff_combine_kernel<__nv_bfloat16, __nv_bfloat16>), ceil_div(items, 4), 128, 0, s, static_cast<const __nv_bfloat16*>(a),
+               static_cast<const __nv_bfloat16*>(gate), gate_stride, lambda, mult, eps, static_cast<__nv_bfloat16*>(out), heads, vdim, items);
   } else {
     set_error("unknown dtype code %d", dtype);
     return kBadArgument;
@@ -155,15 +158,19 @@ TIE_API int tie_diff_combine(int dtype, const float* a, const void* gate, long l
   TIE_RETURN_LAUNCH("diff_combine");
 }
 
-TIE_API int tie_head_talk(int dtype, const float* a, const float* talk, void* out, int tokens, int heads, int kv_heads, int vdim,
+TIE_API int tie_head_talk(int dtype, int a_f32, const void* a, const float* talk, void* out, int tokens, int heads, int kv_heads, int vdim,
                           cudaStream_t s) {
   TIE_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && vdim > 0,
               "head_talk: bad sizes tokens=%d heads=%d/%d vdim=%d", tokens, heads, kv_heads, vdim);
   if (tokens == 0) return kOk;
   if (dtype == TIE_F32) {
-    TIE_LAUNCH((head_talk_kernel<float>), tokens, 256, 0, s, a, talk, static_cast<float*>(out), heads, kv_heads, vdim);
+    TIE_LAUNCH((head_talk_kernel<float, float>), tokens, 256, 0, s, static_cast<const float*>(a), talk, static_cast<float*>(out), heads, kv_heads, vdim);
+  } else if (dtype == TIE_BF16 && a_f32) {
+    TIE_LAUNCH((head_talk_kernel<__nv_bfloat16, float>), tokens, 256, 0, s, static_cast<const float*>(a), talk, static_cast<__nv_bfloat16*>(out),
+               heads, kv_heads, vdim);
   } else if (dtype == TIE_BF16) {
-    TIE_LAUNCH((head_talk_kernel<__nv_bfloat16>), tokens, 256, 0, s, a, talk, static_cast<__nv_bfloat16*>(out), heads, kv_heads, vdim);
+    TIE_LAUNCH((head_talk_kernel<__nv_bfloat16, __nv_bfloat16>), tokens, 256, 0, s, static_cast<const __nv_bfloat16*>(a), talk,
+               static_cast<__nv_bfloat16*>(out), heads, kv_heads, vdim);
   } else {
     set_error("unknown dtype code %d", dtype);
     return kBadArgument;

@@ -1416,9 +1416,9 @@ def _maps_common(q, k_cache, v_cache, out, query_start, context_lens, block_tabl
 
 
 def attention_maps_rows(q, k_cache, v_cache, out, seq_of_row, query_start, context_lens, block_tables, rows: int, q_heads: int, dim: int,
-                        sub_div: int, sub_count: int, scale: float, window: int = 0, chunk: int = 0, softcap: float = 0.0, r1=None,
+                        group: int, sub_div: int, sub_count: int, scale: float, window: int = 0, chunk: int = 0, softcap: float = 0.0, r1=None,
                         r2=None) -> None:
-    """The first `rows` rows of q, each over all keys it sees. Query head h reads kv head h // (q_heads / cached heads) and, of
+    """The first `rows` rows of q, each over all keys it sees. Query head h reads cached head (h // group) % cached heads and, of
     that key row, the `dim` elements from ((h // sub_div) % sub_count) * dim; its softmax weights meet the whole value row.
     `chunk` > 0: a position sees its own chunk of that many positions only; `softcap` > 0: score <- cap tanh(score / cap);
     r1, r2 (float32 [q_heads]): score -= r1 ln(1 + r2 distance). out float32 [T, q_heads * value row]."""
@@ -1427,10 +1427,10 @@ def attention_maps_rows(q, k_cache, v_cache, out, seq_of_row, query_start, conte
     call("tie_attention_maps_rows", dtype_code(q), q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
          seq_of_row.data_ptr(), query_start.data_ptr(), context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1],
          int(rows), S, q_heads, kv_heads, dim, k_cache.shape[3], int(sub_div), int(sub_count), v_dim, k_cache.shape[2], int(window),
-         int(chunk), float(scale), float(softcap), _ptr(r1), _ptr(r2), _stream())
+         int(chunk), float(scale), float(softcap), _ptr(r1), _ptr(r2), int(group), _stream())
 
 
-def attention_maps_split(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads: int, dim: int, sub_div: int,
+def attention_maps_split(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads: int, dim: int, group: int, sub_div: int,
                          sub_count: int, scale: float, seq_list, n_list: int, split_keys: int, max_splits: int, scratch, window: int = 0,
                          chunk: int = 0, softcap: float = 0.0, r1=None, r2=None) -> None:
     """The same for the sequences of seq_list, which bring one row each, their keys cut into splits of split_keys; scratch holds
@@ -1442,31 +1442,57 @@ def attention_maps_split(q, k_cache, v_cache, out, query_start, context_lens, bl
     call("tie_attention_maps_split", dtype_code(q), q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
          query_start.data_ptr(), context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], S, q_heads, kv_heads, dim,
          k_cache.shape[3], int(sub_div), int(sub_count), v_dim, k_cache.shape[2], int(window), int(chunk), float(scale), float(softcap),
-         _ptr(r1), _ptr(r2), seq_list.data_ptr(), n_list, split_keys, max_splits, scratch.data_ptr(), _stream())
+         _ptr(r1), _ptr(r2), int(group), seq_list.data_ptr(), n_list, split_keys, max_splits, scratch.data_ptr(), _stream())
+
+
+def attention_prompt_maps_takes(q, k_cache, v_cache, dim: int) -> bool:
+    """Whether prompt portions of this geometry run on the tensor cores: bfloat16, slices of 64, 128 or 256 for keys and values
+    alike, pages that are powers of two from 8 up, rows in whole 16-byte pieces."""
+    page = k_cache.shape[2]
+    return (q.dtype == torch.bfloat16 and dim in (64, 128, 256) and page >= 8 and page & (page - 1) == 0 and k_cache.shape[3] % dim == 0 and
+            v_cache.shape[3] % dim == 0 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and os.environ.get("TIE_NO_MAPS_TC") != "1")
+
+
+def attention_prompt_maps(q, k_cache, v_cache, out, query_start, context_lens, block_tables, n_seqs: int, max_queries: int, q_heads: int,
+                          kv_heads: int, dim: int, scale: float, v_shift: int = 0, chunk: int = 0, softcap: float = 0.0, r1=None, r2=None) -> None:
+    """Prompt portions on the tensor cores (TMA-fed `mma.sync`, float scores and softmax, weights as two bfloat16 terms) for score
+    maps over slices of wider cached rows: kv head v of `kv_heads` reads cached head v % cached heads, its `dim` key elements from column
+    (v // cached heads) * dim and its `dim` value elements from column ((v // cached heads + v_shift) % slices) * dim, slices = value row / dim;
+    query heads v * (q_heads / kv_heads) .. read kv head v. out bfloat16 [T, q_heads, slices, dim]: the call fills the slice of its value
+    column. At most 16 query heads a kv head."""
+    _dev(q, k_cache, v_cache, out, query_start, context_lens, block_tables, r1, r2)
+    slices = v_cache.shape[3] // dim
+    _need(out.dtype == torch.bfloat16 and out.is_contiguous() and out.shape == (q.shape[0], q_heads * slices * dim),
+          "attention_prompt_maps: out must be bfloat16 [T, q_heads * slices * dim]")
+    _need(q_heads % kv_heads == 0 and q_heads // kv_heads <= 16 and kv_heads % k_cache.shape[1] == 0, "attention_prompt_maps: impossible head counts")
+    call("tie_attention_prompt_maps", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), query_start.data_ptr(),
+         context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], n_seqs, max_queries, q_heads, kv_heads, dim, k_cache.shape[2],
+         k_cache.shape[0], 0, float(scale), k_cache.shape[1], k_cache.shape[3], v_cache.shape[3], int(v_shift), int(chunk), float(softcap),
+         _ptr(r1), _ptr(r2), _stream())
 
 
 def diff_combine(a, gate, lam: float, mult: float, eps: float, out, heads: int, vdim: int) -> None:
-    """a float32 [T, heads * 2 * vdim] (two maps a head): o = a1 - lam a2; out = (o / rms(o)) * mult * sigmoid(gate) per head; gate
-    (None: no gate; rows may be strided) and out [T, heads * vdim] in the compute dtype."""
+    """a [T, 2 * heads * vdim] (map 1 of every head, then map 2; float32 or the compute dtype): o = a1 - lam a2;
+    out = (o / rms(o)) * mult * sigmoid(gate) per head; gate (None: no gate; rows may be strided) and out [T, heads * vdim] in the compute dtype."""
     _dev(a, gate, out)
     T = a.shape[0]
-    _need(a.dtype == torch.float32 and a.is_contiguous() and a.shape == (T, heads * 2 * vdim), "diff_combine: a must be float32 [T, heads * 2 * vdim]")
+    _need(a.dtype in (torch.float32, out.dtype) and a.is_contiguous() and a.shape == (T, heads * 2 * vdim), "diff_combine: a must be [T, 2 * heads * vdim], float32 or out's dtype")
     _need(out.is_contiguous() and out.shape == (T, heads * vdim), "diff_combine: out must be [T, heads * vdim] contiguous")
     _need(gate is None or (gate.dim() == 2 and gate.stride(1) == 1 and gate.shape == out.shape and gate.dtype == out.dtype),
           "diff_combine: gate must be [T, heads * vdim] in out's dtype")
-    call("tie_diff_combine", dtype_code(out), a.data_ptr(), _ptr(gate), gate.stride(0) if gate is not None else 0, float(lam), float(mult),
+    call("tie_diff_combine", dtype_code(out), int(a.dtype == torch.float32), a.data_ptr(), _ptr(gate), gate.stride(0) if gate is not None else 0, float(lam), float(mult),
          float(eps), out.data_ptr(), T, heads, vdim, _stream())
 
 
 def head_talk(a, talk, out, heads: int, kv_heads: int, vdim: int) -> None:
-    """a float32 [T, heads * kv_heads * vdim] (every head's weights on every kv head's values): out[t, h] = sum_g talk[h, g] *
+    """a [T, heads * kv_heads * vdim] (float32 or the compute dtype; every head's weights on every kv head's values): out[t, h] = sum_g talk[h, g] *
     a[t, g, kv head of h]; talk float32 [heads, heads]; out [T, heads * vdim] in the compute dtype."""
     _dev(a, talk, out)
     T = a.shape[0]
-    _need(a.dtype == torch.float32 and a.is_contiguous() and a.shape == (T, heads * kv_heads * vdim), "head_talk: a must be float32 [T, heads * kv_heads * vdim]")
+    _need(a.dtype in (torch.float32, out.dtype) and a.is_contiguous() and a.shape == (T, heads * kv_heads * vdim), "head_talk: a must be [T, heads * kv_heads * vdim], float32 or out's dtype")
     _need(talk.dtype == torch.float32 and talk.is_contiguous() and talk.shape == (heads, heads), "head_talk: talk must be float32 [heads, heads]")
     _need(out.is_contiguous() and out.shape == (T, heads * vdim), "head_talk: out must be [T, heads * vdim] contiguous")
-    call("tie_head_talk", dtype_code(out), a.data_ptr(), talk.data_ptr(), out.data_ptr(), T, heads, kv_heads, vdim, _stream())
+    call("tie_head_talk", dtype_code(out), int(a.dtype == torch.float32), a.data_ptr(), talk.data_ptr(), out.data_ptr(), T, heads, kv_heads, vdim, _stream())
 
 
 # -- a recurrence that blends its inputs with the token before (csrc/time_mix.cu, csrc/delta_rule.cu)

@@ -78,14 +78,15 @@ _SIGNATURES = {
     "tie_side_finish": [P, P, I, I, F, F, P, P, P, I, P, P, P, P, P],
     "tie_rope_pairs_unit_append": [I, P, L, I, I, I, P, I, I, F, P, P, P, P, I, I, I, I, I, I, P],
     "tie_attention_mixed_tc": [P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P, I, I, P, P],
-    "tie_attention_maps_rows": [I, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, I, F, F, P, P, P],
-    "tie_attention_maps_split": [I, P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, F, F, P, P, P, I, I, I, P, P],
+    "tie_attention_maps_rows": [I, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, I, F, F, P, P, I, P],
+    "tie_attention_maps_split": [I, P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, F, F, P, P, I, P, I, I, I, P, P],
+    "tie_attention_prompt_maps": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, I, I, I, F, P, P, P],
     "tie_delta_rule_bonus": [I, P, P, P, P, P, L, P, L, L, P, L, I, I, I, P, P, I, I, I, I, I, I, P, P, P],
     "tie_add_tanh_norm": [I, P, P, P, L, I, F, P, P, L, I, F, P, F, P, P, P, I, I, P],
     "tie_sinusoid_add": [P, P, I, I, F, P],
     "tie_slice_norm_append": [I, P, L, I, I, I, I, I, I, I, P, P, F, P, P, P, I, I, I, I, I, I, P],
-    "tie_diff_combine": [I, P, P, L, F, F, F, P, I, I, I, P],
-    "tie_head_talk": [I, P, P, P, I, I, I, I, P],
+    "tie_diff_combine": [I, I, P, P, L, F, F, F, P, I, I, I, P],
+    "tie_head_talk": [I, I, P, P, P, I, I, I, I, P],
     "tie_token_shift_mix": [I, P, P, I, P, L, L, P, P, P, P, P, L, I, I, P],
     "tie_tanh_rows": [I, P, L, P, L, I, I, P],
     "tie_time_mix_prep": [I, P, P, P, L, P, P, P, P, P, I, I, P],

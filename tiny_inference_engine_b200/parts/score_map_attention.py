@@ -3,7 +3,8 @@ outputs on the kernels of `ops.attention_maps_*`.
 
 `differential_attention`: two score maps a head over the same values.
 
-    q [H, 2, dim], k [G, 2, dim], v [G, vdim] = h Wq^T, h Wk^T, h Wv^T      head by head as [map 1 | map 2]
+    q [H, 2, dim], k [G, 2, dim], v [G, vdim] = h Wq^T, h Wk^T, h Wv^T      head by head as [map 1 | map 2] in the checkpoint;
+                                                                             the engine keeps the rows of Wq map by map
     q, k   = (x / sqrt(mean(x^2) + eps)) * w      per head and map over dim, one weight for all of them (`q.norm`, `k.norm`)
     k, v  -> cache pages (a key row holds both maps of a kv head)
     a_m    = softmax(scale q_m k_m^T over the visible keys) v            m = 1, 2, each a softmax of its own
@@ -62,36 +63,49 @@ class _SliceAttention(Mixer):
     def _name(self, leaf):
         return self.prefix + leaf
 
-    def _stack(self, get, sections):
-        """sections: (leaf, column offset, rows); absent leaves are skipped."""
+    def _stack(self, get, sections, reorder=None):
+        """sections: (leaf, column offset, rows); `reorder`: {leaf: function on the weight} for rows that are kept in another order."""
         first = get(self._name(sections[0][0]))
         stacked = torch.zeros((self.width, self.hidden), dtype=self.dtype, device=first.device)
         for leaf, off, n in sections:
-            stacked[off:off + n] = to_compute(get(self._name(leaf)), self.dtype)
+            w = to_compute(get(self._name(leaf)), self.dtype)
+            stacked[off:off + n] = reorder[leaf](w) if reorder and leaf in reorder else w
         self.gemm_in = ops.bound_gemm(stacked, split_many=False)
         self.w_in = self.gemm_in.w
         self.gemm_o = ops.bound_gemm(to_compute(get(self._name("o")), self.dtype).contiguous(), split_many=True)
         self.w_o = self.gemm_o.w
         self._capacity = None
 
-    def _attend(self, q, cache, ctx, g, out, q_heads, sub_div, sub_count, chunk=0, softcap=0.0, r1=None, r2=None):
-        if ctx.multi_rows > 0:
+    def _attend(self, q, cache, ctx, g, width, q_heads, group, sub_div, sub_count, tensor_cores=None, chunk=0, softcap=0.0, r1=None, r2=None):
+        """The step's rows through attention: [(first row, end row, buffer [T, width])]. Rows of sequences that bring several tokens
+        come first; they go through `tensor_cores(out)` (bfloat16 out) where the caller gives it, else through the CUDA-core kernel
+        (float32 out). Sequences that bring one token go through the split kernel (float32 out)."""
+        T, m, spans = q.shape[0], ctx.multi_rows, []
+        if m > 0 and tensor_cores is not None:
+            out16 = ctx.ws.rows(self.tag + ".attended16", T, width, self.dtype)
+            tensor_cores(out16)
+            spans.append((0, m, out16))
+        out = ctx.ws.rows(self.tag + ".attended", T, width, torch.float32) if ctx.single_count > 0 or len(spans) == 0 else None
+        if m > 0 and tensor_cores is None:
             ops.attention_maps_rows(q, cache.k, cache.v, out, ctx.seq_of_row, ctx.query_start, ctx.context_lens, g.block_tables,
-                                    ctx.multi_rows, q_heads, self.dim, sub_div, sub_count, self.scale, chunk=chunk, softcap=softcap,
-                                    r1=r1, r2=r2)
+                                    m, q_heads, self.dim, group, sub_div, sub_count, self.scale, chunk=chunk, softcap=softcap, r1=r1, r2=r2)
+            spans.append((0, m, out))
         if ctx.single_count > 0:
             longest = ctx.single_max_context if chunk <= 0 else min(ctx.single_max_context, chunk)
-            # enough splits to fill the SMs with warps of (sequence, head), none shorter than SPLIT_KEYS; a constant of the
-            # call, so a token's sums depend on its own context only
-            split_keys = SPLIT_KEYS
+            # splits enough to fill the SMs with warps of (sequence, head, split), none shorter than 32 keys; the split size follows from
+            # the step's longest context and its count of single rows, so a row's sums depend on the batch by their order only
+            want = max(1, (16 * NUM_SMS) // max(1, ctx.single_count * q_heads))
+            split_keys = max(32, -(-math.ceil(longest / want) // 32) * 32)
             while math.ceil(longest / split_keys) > MAX_SPLITS:
                 split_keys *= 2
             max_splits = max(1, math.ceil(longest / split_keys))
             scratch = ctx.ws.flat(self.tag + ".split", ops.attention_split_scratch_floats(ctx.max_seqs, q_heads, cache.v.shape[3], MAX_SPLITS),
                                   torch.float32)
             ops.attention_maps_split(q, cache.k, cache.v, out, ctx.query_start, ctx.context_lens, g.block_tables, q_heads, self.dim,
-                                     sub_div, sub_count, self.scale, ctx.single_seqs, ctx.single_count, split_keys, max_splits, scratch,
+                                     group, sub_div, sub_count, self.scale, ctx.single_seqs, ctx.single_count, split_keys, max_splits, scratch,
                                      chunk=chunk, softcap=softcap, r1=r1, r2=r2)
+            spans.append((m, T, out))
+        return spans
 
     def _project_out(self, heads_out, ctx):
         T = heads_out.shape[0]
@@ -139,7 +153,9 @@ class DifferentialAttention(_SliceAttention):
             sections += [("k", self.k_off, self.k_dim), ("v", self.v_off, self.v_dim)]
         if self.output_gate:
             sections.append(("g", self.g_off, self.o_dim))
-        self._stack(get, sections)
+        H, dim = self.heads, self.dim
+        # queries map by map, [2, H, dim]: the heads that share a key slice are then neighbours, as the attention kernels want them
+        self._stack(get, sections, {"q": lambda w: w.view(H, 2, dim, -1).transpose(0, 1).reshape(2 * H * dim, -1)})
         f32 = lambda leaf: get(self._name(leaf)).to(torch.float32).contiguous()
         self.wq = f32("q.norm")
         self.wk = f32("k.norm") if self.own_kv else None
@@ -159,11 +175,17 @@ class DifferentialAttention(_SliceAttention):
         self.gemm_in(h, proj)
         ops.slice_norm_append(proj, self.q_off, 2 * H, self.k_off, 2 * self.kv_heads, self.v_off, self.v_dim, self.dim, self.wq, self.wk,
                               self.eps, g.slots if self.own_kv else None, cache.k if self.own_kv else None, cache.v if self.own_kv else None)
-        maps = ctx.ws.rows(self.tag + ".maps", T, 2 * H * self.vdim, torch.float32)
-        self._attend(proj[:, :self.q_dim], cache, ctx, g, maps, 2 * H, 1, 2, chunk=self.chunk)
+        q = proj[:, :self.q_dim]
+        per = H // self.kv_heads
+        tensor_cores = None
+        if ctx.multi_rows > 0 and self.dim == self.vdim and per <= 16 and ops.attention_prompt_maps_takes(q, cache.k, cache.v, self.dim):
+            tensor_cores = lambda out: ops.attention_prompt_maps(q, cache.k, cache.v, out, ctx.query_start, ctx.context_lens, g.block_tables,
+                                                                 ctx.multi_seqs, ctx.multi_max_queries, 2 * H, 2 * self.kv_heads, self.dim,
+                                                                 self.scale, chunk=self.chunk)
         heads_out = ctx.ws.rows(self.tag + ".heads", T, self.o_dim, self.dtype)
-        gate = proj[:, self.g_off:self.g_off + self.o_dim] if self.output_gate else None
-        ops.diff_combine(maps, gate, self.lam, 1.0 - self.diff, self.eps, heads_out, H, self.vdim)
+        for lo, hi, maps in self._attend(q, cache, ctx, g, 2 * H * self.vdim, 2 * H, per, H, 2, tensor_cores, chunk=self.chunk):
+            gate = proj[lo:hi, self.g_off:self.g_off + self.o_dim] if self.output_gate else None
+            ops.diff_combine(maps[lo:hi], gate, self.lam, 1.0 - self.diff, self.eps, heads_out[lo:hi], H, self.vdim)
         return self._project_out(heads_out, ctx)
 
 
@@ -213,10 +235,18 @@ class TalkingHeadsAttention(_SliceAttention):
         self.gemm_in(h, proj)
         ops.slice_norm_append(proj, self.q_off, H, self.k_off, G, self.v_off, self.v_dim, self.dim, None, None, self.eps, g.slots,
                               cache.k, cache.v)
-        pairs = ctx.ws.rows(self.tag + ".pairs", T, H * self.v_dim, torch.float32)      # [T, H, G, vdim]
-        self._attend(proj[:, :self.q_dim], cache, ctx, g, pairs, H, H // G, G, softcap=self.softcap, r1=self.r1, r2=self.r2)
+        q = proj[:, :self.q_dim]
+        tensor_cores = None
+        if ctx.multi_rows > 0 and self.dim == self.vdim and H // G <= 16 and ops.attention_prompt_maps_takes(q, cache.k, cache.v, self.dim):
+            def tensor_cores(out):      # one call per distance between a head's own kv head and the kv head whose values it weights
+                for shift in range(G):
+                    ops.attention_prompt_maps(q, cache.k, cache.v, out, ctx.query_start, ctx.context_lens, g.block_tables, ctx.multi_seqs,
+                                              ctx.multi_max_queries, H, G, self.dim, self.scale, v_shift=shift, softcap=self.softcap,
+                                              r1=self.r1, r2=self.r2)
         heads_out = ctx.ws.rows(self.tag + ".heads", T, self.o_dim, self.dtype)
-        ops.head_talk(pairs, self.mix, heads_out, H, G, self.vdim)
+        for lo, hi, pairs in self._attend(q, cache, ctx, g, H * self.v_dim, H, H // G, H // G, G, tensor_cores, softcap=self.softcap,
+                                          r1=self.r1, r2=self.r2):       # pairs [T, H, G, vdim]
+            ops.head_talk(pairs[lo:hi], self.mix, heads_out[lo:hi], H, G, self.vdim)
         return self._project_out(heads_out, ctx)
 
 
