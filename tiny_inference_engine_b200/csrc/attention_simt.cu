@@ -77,6 +77,8 @@ __device__ __forceinline__ void attend_range(const float* __restrict__ qs, const
                                              int lo, int hi, float& m, float& l, float (&acc)[DPL], int k_ld = 0, int k_off = 0,
                                              const ScoreShape shape = ScoreShape{0.0f, 0.0f, 0.0f, 0}) {
   if (k_ld == 0) k_ld = head_dim;
+  // whole pieces of four value elements a lane, each on its own boundary
+  const bool v_quads = DPL % 4 == 0 && v_dim % DPL == 0 && v_ld % 4 == 0 && reinterpret_cast<uintptr_t>(vc) % (4 * sizeof(T)) == 0;
   constexpr int V = Vec16<T>::N;
   const int lane = threadIdx.x & 31;
   const int d0 = lane * DPL;
@@ -112,14 +114,35 @@ __device__ __forceinline__ void attend_range(const float* __restrict__ qs, const
 #pragma unroll
     for (int e = 0; e < DPL; ++e) acc[e] *= corr;
     const int count = min(32, hi - base + 1);
-    for (int jj = 0; jj < count; ++jj) {
-      const float pj = __shfl_sync(0xffffffffu, p, jj);
-      const int rj = __shfl_sync(0xffffffffu, row, jj);
-      if (d0 < v_dim) {
-        const T* vr = vc + static_cast<long long>(rj) * v_ld + d0;
+    if (DPL % 4 == 0 && v_quads) {
+      // a lane's value elements in pieces of four, and the keys four at a time so that their loads are in flight together
+      // (keys beyond `count` have weight 0 and row 0, which is real memory)
+      const bool mine = d0 < v_dim;
+#pragma unroll 4
+      for (int jj = 0; jj < 32; ++jj) {
+        const float pj = __shfl_sync(0xffffffffu, p, jj);       // every lane takes part in the exchanges
+        const int rj = __shfl_sync(0xffffffffu, row, jj);
+        if (mine) {
+          const T* vr = vc + static_cast<long long>(rj) * v_ld + d0;
 #pragma unroll
-        for (int e = 0; e < DPL; ++e)
-          if (d0 + e < v_dim) acc[e] = fmaf(pj, ld(vr + e), acc[e]);
+          for (int e4 = 0; e4 < DPL / 4; ++e4) {
+            float v4[4];
+            load4(vr + 4 * e4, v4);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[4 * e4 + e] = fmaf(pj, v4[e], acc[4 * e4 + e]);
+          }
+        }
+      }
+    } else {
+      for (int jj = 0; jj < count; ++jj) {
+        const float pj = __shfl_sync(0xffffffffu, p, jj);
+        const int rj = __shfl_sync(0xffffffffu, row, jj);
+        if (d0 < v_dim) {
+          const T* vr = vc + static_cast<long long>(rj) * v_ld + d0;
+#pragma unroll
+          for (int e = 0; e < DPL; ++e)
+            if (d0 + e < v_dim) acc[e] = fmaf(pj, ld(vr + e), acc[e]);
+        }
       }
     }
   }
@@ -222,6 +245,149 @@ __global__ void __launch_bounds__(128) attention_split_kernel(AttnArgs a, const 
   }
 }
 
+
+// Single rows in splits, the heads of a cached head together: one block per (sequence, cached head, split), a warp per query head
+// that reads that cached head. A tile of 32 keys (their whole key and value rows) comes into shared memory once and serves every
+// warp: lane j scores key j against its head's slice of the key row, then the lanes share the value row's columns. Leaves
+// (acc, max, sum) where attention_split_kernel leaves them, for the same merge.
+constexpr int kGroupTile = 32;
+
+template <typename T, int DPL>
+__global__ void __launch_bounds__(1024) attention_group_split_kernel(AttnArgs a, const int* __restrict__ seq_list, int n_list,
+                                                                     int split_keys, int max_splits, float* __restrict__ scratch,
+                                                                     int k_pad) {
+  pdl_sync();
+  extern __shared__ __align__(16) uint8_t group_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const int li = blockIdx.x / a.kv_heads, c = blockIdx.x % a.kv_heads, split = blockIdx.y;
+  const int k_ld = a.k_ld ? a.k_ld : a.head_dim, v_ld = a.v_ld ? a.v_ld : a.v_dim;
+  // shared memory: q of every warp (float), the tile's cache rows, K tile (rows padded by k_pad elements), V tile
+  float* qs_all = reinterpret_cast<float*>(group_smem);
+  int* rows = reinterpret_cast<int*>(qs_all + warps * a.head_dim);
+  T* k_tile = reinterpret_cast<T*>(reinterpret_cast<uint8_t*>(rows + kGroupTile) + ((16 - (warps * a.head_dim + kGroupTile) * 4 % 16) % 16));
+  const int k_row = k_ld + k_pad;
+  T* v_tile = k_tile + kGroupTile * k_row;
+  const int s = seq_list[li];
+  const int t = a.query_start[s];
+  const int pos = a.context_lens[s] - 1;
+  const int lo0 = first_visible(pos, a.window, a.chunk);
+  const int lo = lo0 + split * split_keys;
+  if (lo > pos) return;                      // the whole block: this sequence has fewer splits
+  const int hi = split == max_splits - 1 ? pos : min(pos, lo + split_keys - 1);
+  // the warp's query head: the heads h with (h / group) % kv_heads == c, in order
+  const int group = a.group > 0 ? a.group : a.q_heads / a.kv_heads;
+  const int h = ((warp / group) * a.kv_heads + c) * group + warp % group;
+  float* qs = qs_all + warp * a.head_dim;
+  const T* qv = static_cast<const T*>(a.q) + static_cast<long long>(t) * a.q_stride + static_cast<long long>(h) * a.head_dim;
+  for (int d = lane; d < a.head_dim; d += 32) qs[d] = ld(qv + d);
+  const int k_off = key_offset(a, h);
+  const ScoreShape shape = score_shape(a, h, pos);
+  const int* table = a.block_tables + static_cast<long long>(s) * a.max_blocks;
+  const T* kc = static_cast<const T*>(a.k_cache);
+  const T* vc = static_cast<const T*>(a.v_cache);
+  constexpr int V = Vec16<T>::N;
+  const bool k_vec = k_ld % V == 0 && k_pad % V == 0 && reinterpret_cast<uintptr_t>(kc) % 16 == 0;
+  const bool v_vec = v_ld % V == 0 && reinterpret_cast<uintptr_t>(vc) % 16 == 0;
+  const bool dot_vec = k_vec && a.head_dim % V == 0;
+  const int d0 = lane * DPL;
+  float m = -INFINITY, l = 0.0f, acc[DPL] = {};
+  for (int base = lo; base <= hi; base += kGroupTile) {
+    __syncthreads();                          // everyone is through with the tile before
+    if (threadIdx.x < kGroupTile) {
+      const int j = base + threadIdx.x;
+      rows[threadIdx.x] = j <= hi ? (table[j / a.page_size] * a.kv_heads + c) * a.page_size + j % a.page_size : -1;
+    }
+    __syncthreads();
+    if (k_vec) {
+      const int pieces = k_ld / V;
+      for (int i = threadIdx.x; i < kGroupTile * pieces; i += blockDim.x) {
+        const int kk = i / pieces, p = (i % pieces) * V;
+        uint4 val = make_uint4(0u, 0u, 0u, 0u);
+        if (rows[kk] >= 0) val = *reinterpret_cast<const uint4*>(kc + static_cast<long long>(rows[kk]) * k_ld + p);
+        *reinterpret_cast<uint4*>(k_tile + kk * k_row + p) = val;
+      }
+    } else {
+      for (int i = threadIdx.x; i < kGroupTile * k_ld; i += blockDim.x) {
+        const int kk = i / k_ld, p = i % k_ld;
+        k_tile[kk * k_row + p] = rows[kk] >= 0 ? kc[static_cast<long long>(rows[kk]) * k_ld + p] : T(0.0f);
+      }
+    }
+    if (v_vec) {
+      const int pieces = v_ld / V;
+      for (int i = threadIdx.x; i < kGroupTile * pieces; i += blockDim.x) {
+        const int kk = i / pieces, p = (i % pieces) * V;
+        uint4 val = make_uint4(0u, 0u, 0u, 0u);
+        if (rows[kk] >= 0) val = *reinterpret_cast<const uint4*>(vc + static_cast<long long>(rows[kk]) * v_ld + p);
+        *reinterpret_cast<uint4*>(v_tile + kk * v_ld + p) = val;
+      }
+    } else {
+      for (int i = threadIdx.x; i < kGroupTile * v_ld; i += blockDim.x) {
+        const int kk = i / v_ld, p = i % v_ld;
+        v_tile[kk * v_ld + p] = rows[kk] >= 0 ? vc[static_cast<long long>(rows[kk]) * v_ld + p] : T(0.0f);
+      }
+    }
+    __syncthreads();
+    const int j = base + lane;
+    const bool valid = j <= hi;
+    float sc = -INFINITY;
+    if (valid) {
+      const T* kr = k_tile + lane * k_row + k_off;
+      float dot = 0.0f;
+      if (dot_vec) {
+        for (int d = 0; d < a.head_dim; d += V) {
+          Vec16<T> kv;
+          kv.load(kr + d);
+#pragma unroll
+          for (int e = 0; e < V; ++e) dot = fmaf(qs[d + e], kv.v[e], dot);
+        }
+      } else {
+        for (int d = 0; d < a.head_dim; ++d) dot = fmaf(qs[d], ld(kr + d), dot);
+      }
+      sc = a.scale * dot;
+      if (shape.softcap > 0.0f) sc = shape.softcap * tanhf(sc / shape.softcap);
+      if (shape.r1 != 0.0f) sc -= shape.r1 * log1pf(shape.r2 * static_cast<float>(pos - j));
+    }
+    const float m_new = fmaxf(m, warp_max(sc));
+    const float corr = expf(m - m_new);
+    const float p = valid ? expf(sc - m_new) : 0.0f;
+    l = l * corr + warp_sum(p);
+    m = m_new;
+#pragma unroll
+    for (int e = 0; e < DPL; ++e) acc[e] *= corr;
+#pragma unroll 4
+    for (int jj = 0; jj < kGroupTile; ++jj) {
+      const float pj = __shfl_sync(0xffffffffu, p, jj);
+      const T* vr = v_tile + jj * v_ld + d0;
+#pragma unroll
+      for (int e = 0; e < DPL; ++e)
+        if (d0 + e < a.v_dim) acc[e] = fmaf(pj, ld(vr + e), acc[e]);
+    }
+  }
+  float* dst = scratch + ((static_cast<long long>(li) * a.q_heads + h) * max_splits + split) * (a.v_dim + 2);
+  if (d0 < a.v_dim) {
+#pragma unroll
+    for (int e = 0; e < DPL; ++e)
+      if (d0 + e < a.v_dim) dst[d0 + e] = acc[e];
+  }
+  if (lane == 0) {
+    dst[a.v_dim] = m;
+    dst[a.v_dim + 1] = l;
+  }
+}
+
+// The grouped kernel's launch geometry for `a`, or 0 bytes when it does not fit (then the kernel above serves).
+template <typename T>
+static size_t group_split_smem(const AttnArgs& a, int* warps, int* k_pad) {
+  const int per = a.q_heads / a.kv_heads;
+  const int k_ld = a.k_ld ? a.k_ld : a.head_dim, v_ld = a.v_ld ? a.v_ld : a.v_dim;
+  *warps = per;
+  *k_pad = 16 / static_cast<int>(sizeof(T));        // rows a 16-byte piece apart in the banks: lanes read a column of 16-byte pieces
+  if (per > 32 || a.v_ld != 0) return 0;
+  const size_t bytes = static_cast<size_t>(per) * a.head_dim * 4 + kGroupTile * 4 + 16 +
+                       static_cast<size_t>(kGroupTile) * (k_ld + *k_pad + v_ld) * sizeof(T);
+  return bytes <= 96 * 1024 ? bytes : 0;
+}
+
 // Merge of the splits of one (sequence, head), in split order: one block each. The weights
 // exp(m_i - m) of the splits are computed once into shared memory, then every thread sums its
 // dims over the splits.
@@ -278,8 +444,10 @@ __global__ void __launch_bounds__(kMergeThreads) attention_merge_kernel(AttnArgs
 
 template <typename T>
 int launch_attention(const AttnArgs& a, const int* row_seq_unused, const int* seq_list, int n_list, int split_keys,
-                     int max_splits, float* scratch, int rows_kernel, cudaStream_t s) {
+                     int max_splits, float* scratch, int rows_kernel, cudaStream_t s, bool grouped = false) {
   (void)row_seq_unused;
+  int group_warps = 0, k_pad = 0;
+  const size_t group_smem = grouped && !rows_kernel ? group_split_smem<T>(a, &group_warps, &k_pad) : 0;
   const int warps = 4;
   const size_t smem = static_cast<size_t>(warps) * a.head_dim * sizeof(float);
   AttnArgs merge_args = a;            // the merge kernel sees output heads only
@@ -293,6 +461,12 @@ int launch_attention(const AttnArgs& a, const int* row_seq_unused, const int* se
     } else {                                                                                                     \
       const long long items = static_cast<long long>(n_list) * a.q_heads;                                        \
       if (items > 0) {                                                                                           \
+        if (group_smem > 0) {                                                                                    \
+          if (group_smem > 48 * 1024)                                                                            \
+            cudaFuncSetAttribute(attention_group_split_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); \
+          TIE_LAUNCH((attention_group_split_kernel<T, D>), dim3(n_list * a.kv_heads, max_splits), group_warps * 32, group_smem, s, \
+              a, seq_list, n_list, split_keys, max_splits, scratch, k_pad);                                      \
+        } else                                                                                                   \
         TIE_LAUNCH((attention_split_kernel<T, D>), dim3(ceil_div(items, warps), max_splits), warps * 32, smem, s,           \
             a, seq_list, n_list, split_keys, max_splits, scratch);                                               \
         TIE_LAUNCH((attention_merge_kernel<T>), static_cast<int>(items), kMergeThreads, 0, s, merge_args, seq_list, n_list, split_keys, \
@@ -467,9 +641,9 @@ TIE_API int tie_attention_maps_split(int dtype, const void* q, long long q_strid
   if (const int st = check_attn(a, true)) return st;
   TIE_REQUIRE(split_keys > 0 && max_splits > 0 && max_splits <= kMergeMaxSplits && scratch != nullptr,
               "attention split: bad split geometry (at most %d splits)", kMergeMaxSplits);
-  if (dtype == TIE_F32) return launch_attention<float>(a, nullptr, seq_list, n_list, split_keys, max_splits, scratch, 0, s);
+  if (dtype == TIE_F32) return launch_attention<float>(a, nullptr, seq_list, n_list, split_keys, max_splits, scratch, 0, s, true);
   if (dtype == TIE_BF16)
-    return launch_attention<__nv_bfloat16>(a, nullptr, seq_list, n_list, split_keys, max_splits, scratch, 0, s);
+    return launch_attention<__nv_bfloat16>(a, nullptr, seq_list, n_list, split_keys, max_splits, scratch, 0, s, true);
   set_error("attention: unknown dtype code %d", dtype);
   return kBadArgument;
 }

@@ -142,6 +142,20 @@ inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
   cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);   // errors surface in cudaGetLastError()
 }
 
+// The same without the early start: the kernel's blocks are placed when the kernels ahead have drained. For kernels of few,
+// long-running blocks: placed early, beside a kernel that still fills the GPU, they pile up on the SMs that have room first
+// instead of spreading one to an SM.
+template <typename... KArgs, typename... Args>
+inline void launch_kernel_alone(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cfg.numAttrs = 0;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace tie
 
 #define TIE_LAUNCH(kernel, grid, block, smem, stream, ...) \

@@ -1,10 +1,11 @@
 // What stands around the plain recurrence (delta_rule.cu, read-first mode) for a mixer that blends every input with
 // the token before:
 //
-//   token_shift_mix   out[s][t] = h[t] + (h[t - 1] - h[t]) * mu[s] for each of n_mix blends; the row before the first
-//                     row of a sequence's portion is the one its state slot keeps (zeros at position 0).
-//   tanh_rows         float rows -> tanh in the compute type (the inner activation of a two-step projection)
-//   time_mix_prep     r, k, v (compute type) -> float rows; decay = exp(-exp(z + w0)) in place, float
+//   token_shift_concat  out[t] = [h[t] | h[t - 1]]; the row before the first row of a sequence's portion is the one its state
+//                       slot keeps (zeros at position 0). A blend h + (h' - h) * mu times a weight W is [W (1 - mu) | W mu] times
+//                       this row (the factors scale W's columns), so all blends' projections are one matrix product.
+//   time_mix_prep       r, k, v (compute type) -> float rows; decay = exp(-exp(w2 tanh(inner) + w0)), float: the second step of
+//                       the decay's projection runs here, over a few dozen inner channels
 //   time_mix_out      (o / rms(o) per head) * w[h, :] * silu(gate) in the compute type; the sequence's last row of h
 //                     becomes the row that its slot keeps
 #include <math.h>
@@ -14,51 +15,45 @@
 namespace tie {
 
 template <typename T>
-__global__ void __launch_bounds__(256) token_shift_mix_kernel(const T* __restrict__ h, const float* __restrict__ mu, int n_mix,
-                                                              const float* __restrict__ state, long long state_stride,
-                                                              long long prev_off, const int* __restrict__ seq_of_row,
-                                                              const int* __restrict__ query_start,
-                                                              const int* __restrict__ positions, const int* __restrict__ state_slots,
-                                                              T* __restrict__ out, long long out_stride, int D) {
+__global__ void __launch_bounds__(256) token_shift_concat_kernel(const T* __restrict__ h, const float* __restrict__ state,
+                                                                 long long state_stride, long long prev_off,
+                                                                 const int* __restrict__ seq_of_row, const int* __restrict__ query_start,
+                                                                 const int* __restrict__ positions, const int* __restrict__ state_slots,
+                                                                 T* __restrict__ out, int D) {
   pdl_sync();
   const long long t = blockIdx.x;
   const int s = seq_of_row[t];
   const bool first = t == query_start[s];
   const int slot = state_slots[s];
   const float* kept = (first && positions[t] > 0 && slot >= 0) ? state + slot * state_stride + prev_off : nullptr;
+  T* row = out + t * 2 * D;
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    const float cur = ld(h + t * D + d);
-    const float before = first ? (kept ? kept[d] : 0.0f) : ld(h + (t - 1) * D + d);
-    const float diff = before - cur;
-    for (int m = 0; m < n_mix; ++m) st(out + t * out_stride + static_cast<long long>(m) * D + d, fmaf(diff, mu[m * D + d], cur));
+    row[d] = h[t * D + d];
+    if (first) st(row + D + d, kept ? kept[d] : 0.0f);
+    else row[D + d] = h[(t - 1) * D + d];
   }
 }
 
+// One block a token: tanh of the inner channels once into shared memory, then a thread a decay channel.
 template <typename T>
-__global__ void __launch_bounds__(256) tanh_rows_kernel(const float* __restrict__ x, long long x_stride, T* __restrict__ out,
-                                                        long long out_stride, int cols, long long total) {
+__global__ void __launch_bounds__(256) time_mix_prep_kernel(const T* __restrict__ proj, long long stride, int r_off, int k_off, int v_off,
+                                                            int inner_off, int rank, const float* __restrict__ w2t,
+                                                            const float* __restrict__ w0, float* __restrict__ rn, float* __restrict__ kn,
+                                                            float* __restrict__ vn, float* __restrict__ decay, int n) {
   pdl_sync();
-  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= total) return;
-  const long long t = i / cols;
-  const int c = static_cast<int>(i % cols);
-  st(out + t * out_stride + c, tanhf(x[t * x_stride + c]));
-}
-
-template <typename T>
-__global__ void __launch_bounds__(256) time_mix_prep_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v,
-                                                            long long in_stride, const float* __restrict__ w0, float* __restrict__ rn,
-                                                            float* __restrict__ kn, float* __restrict__ vn, float* __restrict__ decay,
-                                                            int n, long long total) {
-  pdl_sync();
-  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= total) return;
-  const long long t = i / n;
-  const int c = static_cast<int>(i % n);
-  rn[i] = ld(r + t * in_stride + c);
-  kn[i] = ld(k + t * in_stride + c);
-  vn[i] = ld(v + t * in_stride + c);
-  decay[i] = expf(-expf(decay[i] + w0[c]));
+  extern __shared__ float inner[];
+  const long long t = blockIdx.x;
+  const T* row = proj + t * stride;
+  for (int j = threadIdx.x; j < rank; j += blockDim.x) inner[j] = tanhf(ld(row + inner_off + j));
+  __syncthreads();
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    rn[t * n + c] = ld(row + r_off + c);
+    kn[t * n + c] = ld(row + k_off + c);
+    vn[t * n + c] = ld(row + v_off + c);
+    float z = 0.0f;
+    for (int j = 0; j < rank; ++j) z = fmaf(w2t[static_cast<long long>(j) * n + c], inner[j], z);
+    decay[t * n + c] = expf(-expf(z + w0[c]));
+  }
 }
 
 template <typename T>
@@ -108,42 +103,30 @@ using namespace tie;
     }                                            \
   } while (0)
 
-TIE_API int tie_token_shift_mix(int dtype, const void* h, const float* mu, int n_mix, const float* state, long long state_stride,
-                                long long prev_off, const int* seq_of_row, const int* query_start, const int* positions,
-                                const int* state_slots, void* out, long long out_stride, int tokens, int D, cudaStream_t s) {
-  TIE_REQUIRE(tokens >= 0 && D > 0 && n_mix > 0 && out_stride >= static_cast<long long>(n_mix) * D, "token_shift_mix: bad sizes");
+TIE_API int tie_token_shift_concat(int dtype, const void* h, const float* state, long long state_stride, long long prev_off,
+                                   const int* seq_of_row, const int* query_start, const int* positions, const int* state_slots,
+                                   void* out, int tokens, int D, cudaStream_t s) {
+  TIE_REQUIRE(tokens >= 0 && D > 0, "token_shift_concat: bad sizes");
   if (tokens == 0) return kOk;
   TIE_BY_DTYPE(dtype,
-               TIE_LAUNCH((token_shift_mix_kernel<float>), tokens, 256, 0, s, static_cast<const float*>(h), mu, n_mix, state, state_stride,
-                          prev_off, seq_of_row, query_start, positions, state_slots, static_cast<float*>(out), out_stride, D),
-               TIE_LAUNCH((token_shift_mix_kernel<__nv_bfloat16>), tokens, 256, 0, s, static_cast<const __nv_bfloat16*>(h), mu, n_mix, state,
-                          state_stride, prev_off, seq_of_row, query_start, positions, state_slots, static_cast<__nv_bfloat16*>(out),
-                          out_stride, D));
-  TIE_RETURN_LAUNCH("token_shift_mix");
+               TIE_LAUNCH((token_shift_concat_kernel<float>), tokens, 256, 0, s, static_cast<const float*>(h), state, state_stride, prev_off,
+                          seq_of_row, query_start, positions, state_slots, static_cast<float*>(out), D),
+               TIE_LAUNCH((token_shift_concat_kernel<__nv_bfloat16>), tokens, 256, 0, s, static_cast<const __nv_bfloat16*>(h), state,
+                          state_stride, prev_off, seq_of_row, query_start, positions, state_slots, static_cast<__nv_bfloat16*>(out), D));
+  TIE_RETURN_LAUNCH("token_shift_concat");
 }
 
-TIE_API int tie_tanh_rows(int dtype, const float* x, long long x_stride, void* out, long long out_stride, int tokens, int cols,
-                          cudaStream_t s) {
-  TIE_REQUIRE(tokens >= 0 && cols > 0, "tanh_rows: bad sizes");
-  const long long total = static_cast<long long>(tokens) * cols;
-  if (total == 0) return kOk;
+TIE_API int tie_time_mix_prep(int dtype, const void* proj, long long stride, int r_off, int k_off, int v_off, int inner_off, int rank,
+                              const float* w2t, const float* w0, float* rn, float* kn, float* vn, float* decay, int tokens, int n,
+                              cudaStream_t s) {
+  TIE_REQUIRE(tokens >= 0 && n > 0 && rank > 0 && rank <= 8192, "time_mix_prep: bad sizes tokens=%d n=%d inner=%d", tokens, n, rank);
+  if (tokens == 0) return kOk;
+  const size_t smem = static_cast<size_t>(rank) * sizeof(float);
   TIE_BY_DTYPE(dtype,
-               TIE_LAUNCH((tanh_rows_kernel<float>), ceil_div(total, 256), 256, 0, s, x, x_stride, static_cast<float*>(out), out_stride, cols, total),
-               TIE_LAUNCH((tanh_rows_kernel<__nv_bfloat16>), ceil_div(total, 256), 256, 0, s, x, x_stride, static_cast<__nv_bfloat16*>(out),
-                          out_stride, cols, total));
-  TIE_RETURN_LAUNCH("tanh_rows");
-}
-
-TIE_API int tie_time_mix_prep(int dtype, const void* r, const void* k, const void* v, long long in_stride, const float* w0, float* rn,
-                              float* kn, float* vn, float* decay, int tokens, int n, cudaStream_t s) {
-  TIE_REQUIRE(tokens >= 0 && n > 0, "time_mix_prep: bad sizes");
-  const long long total = static_cast<long long>(tokens) * n;
-  if (total == 0) return kOk;
-  TIE_BY_DTYPE(dtype,
-               TIE_LAUNCH((time_mix_prep_kernel<float>), ceil_div(total, 256), 256, 0, s, static_cast<const float*>(r), static_cast<const float*>(k),
-                          static_cast<const float*>(v), in_stride, w0, rn, kn, vn, decay, n, total),
-               TIE_LAUNCH((time_mix_prep_kernel<__nv_bfloat16>), ceil_div(total, 256), 256, 0, s, static_cast<const __nv_bfloat16*>(r),
-                          static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), in_stride, w0, rn, kn, vn, decay, n, total));
+               TIE_LAUNCH((time_mix_prep_kernel<float>), tokens, 256, smem, s, static_cast<const float*>(proj), stride, r_off, k_off, v_off,
+                          inner_off, rank, w2t, w0, rn, kn, vn, decay, n),
+               TIE_LAUNCH((time_mix_prep_kernel<__nv_bfloat16>), tokens, 256, smem, s, static_cast<const __nv_bfloat16*>(proj), stride, r_off,
+                          k_off, v_off, inner_off, rank, w2t, w0, rn, kn, vn, decay, n));
   TIE_RETURN_LAUNCH("time_mix_prep");
 }
 

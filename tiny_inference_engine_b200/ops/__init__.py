@@ -1497,39 +1497,30 @@ def head_talk(a, talk, out, heads: int, kv_heads: int, vdim: int) -> None:
 
 # -- a recurrence that blends its inputs with the token before (csrc/time_mix.cu, csrc/delta_rule.cu)
 
-def token_shift_mix(h, mu, state, prev_off: int, ctx, out) -> None:
-    """out[t, m * D:(m + 1) * D] = h[t] + (h[t - 1] - h[t]) * mu[m]; the row before a portion's first row comes from the sequence's
-    row of `state` (float32 [slots, floats], at prev_off; zeros at position 0). h [T, D] and out [T, n * D] in the compute dtype, mu float32 [n, D]."""
-    _dev(h, mu, state, out)
+def token_shift_concat(h, state, prev_off: int, ctx, out) -> None:
+    """out[t] = [h[t] | h[t - 1]]; the row before a portion's first row comes from the sequence's row of `state` (float32
+    [slots, floats], at prev_off; zeros at position 0). h [T, D] and out [T, 2 D] in the compute dtype, contiguous."""
+    _dev(h, state, out)
     T, D = h.shape
-    n = mu.shape[0]
-    _need(h.is_contiguous() and out.dtype == h.dtype and out.stride(1) == 1 and out.shape == (T, n * D), "token_shift_mix: out must be [T, n * D] in h's dtype")
-    _need(mu.dtype == torch.float32 and mu.is_contiguous() and mu.shape == (n, D), "token_shift_mix: mu must be float32 [n, D]")
-    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1 and state.shape[1] >= prev_off + D, "token_shift_mix: state rows too short")
-    call("tie_token_shift_mix", dtype_code(h), h.data_ptr(), mu.data_ptr(), n, state.data_ptr(), state.stride(0), prev_off,
-         ctx.seq_of_row.data_ptr(), ctx.query_start.data_ptr(), ctx.positions.data_ptr(), ctx.state_slots.data_ptr(), out.data_ptr(),
-         out.stride(0), T, D, _stream())
+    _need(h.is_contiguous() and out.dtype == h.dtype and out.is_contiguous() and out.shape == (T, 2 * D), "token_shift_concat: out must be [T, 2 D] in h's dtype")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1 and state.shape[1] >= prev_off + D, "token_shift_concat: state rows too short")
+    call("tie_token_shift_concat", dtype_code(h), h.data_ptr(), state.data_ptr(), state.stride(0), prev_off, ctx.seq_of_row.data_ptr(),
+         ctx.query_start.data_ptr(), ctx.positions.data_ptr(), ctx.state_slots.data_ptr(), out.data_ptr(), T, D, _stream())
 
 
-def tanh_rows(x, out) -> None:
-    """out[:, :cols] = tanh(x) (x float32 [T, cols], rows may be strided; out in the compute dtype, at least as wide)."""
-    _dev(x, out)
-    _need(x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1 and out.dim() == 2 and out.stride(1) == 1 and
-          out.shape[0] == x.shape[0] and out.shape[1] >= x.shape[1], "tanh_rows: x float32 [T, cols], out [T, >= cols]")
-    call("tie_tanh_rows", dtype_code(out), x.data_ptr(), x.stride(0), out.data_ptr(), out.stride(0), x.shape[0], x.shape[1], _stream())
-
-
-def time_mix_prep(r, k, v, w0, rn, kn, vn, decay) -> None:
-    """r, k, v [T, n] (compute dtype, one row stride) as float32 rows rn, kn, vn; decay (float32 [T, n], holding the raw
-    projection) <- exp(-exp(decay + w0)), w0 float32 [n]."""
-    _dev(r, k, v, w0, rn, kn, vn, decay)
+def time_mix_prep(proj, r_off: int, k_off: int, v_off: int, inner_off: int, w2t, w0, rn, kn, vn, decay) -> None:
+    """Columns r_off.., k_off.., v_off.. of `proj` (n each) as float32 rows rn, kn, vn; decay = exp(-exp(tanh(inner) w2t + w0)) with
+    `inner` the columns inner_off.. of proj (as many as w2t has rows), w2t float32 [inner, n], w0 float32 [n]."""
+    _dev(proj, w2t, w0, rn, kn, vn, decay)
     T, n = decay.shape
-    _need(all(t.shape == (T, n) and t.stride(1) == 1 and t.stride(0) == r.stride(0) and t.dtype == r.dtype for t in (r, k, v)),
-          "time_mix_prep: r, k, v must be [T, n] alike")
-    _need(all(t.dtype == torch.float32 and t.is_contiguous() and t.shape == (T, n) for t in (rn, kn, vn, decay)) and
-          w0.dtype == torch.float32 and w0.numel() == n, "time_mix_prep: float32 [T, n] outputs, w0 float32 [n]")
-    call("tie_time_mix_prep", dtype_code(r), r.data_ptr(), k.data_ptr(), v.data_ptr(), r.stride(0), w0.data_ptr(), rn.data_ptr(),
-         kn.data_ptr(), vn.data_ptr(), decay.data_ptr(), T, n, _stream())
+    rank = w2t.shape[0]
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[0] == T and proj.shape[1] >= max(r_off, k_off, v_off) + n and
+          proj.shape[1] >= inner_off + rank, "time_mix_prep: proj too narrow")
+    _need(all(t.dtype == torch.float32 and t.is_contiguous() and t.shape == (T, n) for t in (rn, kn, vn, decay)) and w0.dtype == torch.float32 and
+          w0.numel() == n and w2t.dtype == torch.float32 and w2t.is_contiguous() and w2t.shape == (rank, n),
+          "time_mix_prep: float32 [T, n] outputs, w2t float32 [inner, n], w0 float32 [n]")
+    call("tie_time_mix_prep", dtype_code(proj), proj.data_ptr(), proj.stride(0), r_off, k_off, v_off, inner_off, rank, w2t.data_ptr(), w0.data_ptr(),
+         rn.data_ptr(), kn.data_ptr(), vn.data_ptr(), decay.data_ptr(), T, n, _stream())
 
 
 def delta_rule_bonus(qn, kn, vn, decay, bonus, state, ctx, heads: int, dim: int, out) -> None:

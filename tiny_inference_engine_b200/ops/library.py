@@ -87,9 +87,8 @@ _SIGNATURES = {
     "tie_slice_norm_append": [I, P, L, I, I, I, I, I, I, I, P, P, F, P, P, P, I, I, I, I, I, I, P],
     "tie_diff_combine": [I, I, P, P, L, F, F, F, P, I, I, I, P],
     "tie_head_talk": [I, I, P, P, P, I, I, I, I, P],
-    "tie_token_shift_mix": [I, P, P, I, P, L, L, P, P, P, P, P, L, I, I, P],
-    "tie_tanh_rows": [I, P, L, P, L, I, I, P],
-    "tie_time_mix_prep": [I, P, P, P, L, P, P, P, P, P, I, I, P],
+    "tie_token_shift_concat": [I, P, P, L, L, P, P, P, P, P, I, I, P],
+    "tie_time_mix_prep": [I, P, L, I, I, I, I, I, P, P, P, P, P, P, I, I, P],
     "tie_time_mix_out": [I, P, P, L, P, F, P, I, I, I, P, I, P, L, L, P, P, P, P],
     "tie_two_branch_unit": [I, P, P, L, F, F, P],
     "tie_attention_mixed": [I, P, L, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P, I, I, I, P, P],

@@ -9,8 +9,11 @@ x_s = h + (h' - h) * mu_s for s in r, k, v, g, w. Then, per head of `dim` key an
     S      <- diag(w_t) S + k_t v_t^T                                    S float32 [dim, dim], zero at the start of a sequence
     out     = ((o / sqrt(mean(o^2) + eps) per head) * norm * gate) Wo^T   `norm` has a weight per head and channel
 
-A request's state is one float32 row in a state slot: S of every head, then the last row of h it has seen. The blends,
-the decay from its raw projection on, S and the read-out's norm are float32 in either compute dtype. The recurrence is the
+A request's state is one float32 row in a state slot: S of every head, then the last row of h it has seen. The decay from
+its raw projection on, S and the read-out's norm are float32 in either compute dtype. The engine never forms the blends: with
+W (1 - mu) and W mu, the columns of W scaled by the blend's factors (in float32, once, when the weights are bound),
+x_s W^T = [h | h'] [W (1 - mu_s) | W mu_s]^T, so the five projections are ONE matrix product over the rows [h | h'], the
+weights stacked; the second step of the decay's projection, over its few inner channels, runs in the kernel that forms the decays. The recurrence is the
 engine's plain recurrence kernel in its read-first mode. The inner size of the decay projection comes from its tensors'
 shapes (`decay_rank`).
 """
@@ -59,18 +62,19 @@ class TokenShiftRecurrence(Mixer):
         return t
 
     def bind(self, get):
-        name = self._name
+        name, D, n = self._name, self.hidden, self.n
         f32 = lambda leaf: get(name(leaf)).to(torch.float32).contiguous()
-        self.mu = torch.stack([f32("mu." + s) for s in BLENDS]).contiguous()
-        self.gemms = [ops.bound_gemm(to_compute(get(name(s)), self.dtype).contiguous(), split_many=False) for s in ("r", "k", "v", "g")]
-        w1 = to_compute(get(name("w1")), self.dtype)
-        w1p = torch.zeros((self.rank8, self.hidden), dtype=self.dtype, device=w1.device)       # rows padded: tanh(0) = 0 meets zero columns
-        w1p[:self.rank] = w1
-        self.gemm_w1 = ops.bound_gemm(w1p, split_many=False)
-        w2 = to_compute(get(name("w2")), self.dtype)
-        w2p = torch.zeros((self.n, self.rank8), dtype=self.dtype, device=w2.device)
-        w2p[:, :self.rank] = w2
-        self.gemm_w2 = ops.bound_gemm(w2p, split_many=False)
+        n8 = _up8(n)
+        self.offs = {s: i * n8 for i, s in enumerate(("r", "k", "v", "g"))}       # columns of the stacked product
+        self.inner_off = 4 * n8
+        self.width = self.inner_off + self.rank8
+        stacked = torch.zeros((self.width, 2 * D), dtype=torch.float32, device=get(name("r")).device)
+        for s, leaf, off, rows in [(s, s, self.offs[s], n) for s in ("r", "k", "v", "g")] + [("w", "w1", self.inner_off, self.rank)]:
+            w, mu = f32(leaf), f32("mu." + s)
+            stacked[off:off + rows, :D] = w * (1.0 - mu)[None, :]
+            stacked[off:off + rows, D:] = w * mu[None, :]
+        self.gemm_in = ops.bound_gemm(stacked.to(self.dtype).contiguous(), split_many=False)
+        self.w2t = f32("w2").t().contiguous()                 # [inner, n]: a thread a decay channel reads it coalesced
         self.gemm_o = ops.bound_gemm(to_compute(get(name("o")), self.dtype).contiguous(), split_many=True)
         self.w0, self.bonus, self.norm_w = f32("w0"), f32("u").reshape(-1).contiguous(), f32("norm")
         self._capacity = None
@@ -82,23 +86,16 @@ class TokenShiftRecurrence(Mixer):
         T, D, n = h.shape[0], self.hidden, self.n
         if state is None:
             raise InvalidArgument("the token-shift recurrence needs state slots (make the cache with `make_cache`)")
-        blends = ctx.ws.rows("tmix.blends", T, len(BLENDS) * D, self.dtype)
-        ops.token_shift_mix(h, self.mu, state, self.state_floats, ctx, blends)
-        proj = [ctx.ws.rows("tmix.proj." + s, T, n, self.dtype) for s in BLENDS[:4]]
-        for i, gemm in enumerate(self.gemms):
-            gemm(blends[:, i * D:(i + 1) * D], proj[i])
-        inner = ctx.ws.rows("tmix.inner", T, self.rank8, torch.float32)
-        self.gemm_w1(blends[:, 4 * D:5 * D], inner)
-        inner_act = ctx.ws.rows("tmix.inner.act", T, self.rank8, self.dtype)
-        ops.tanh_rows(inner, inner_act)
-        decay = ctx.ws.rows("tmix.decay", T, n, torch.float32)
-        self.gemm_w2(inner_act, decay)
-        rn, kn, vn = (ctx.ws.rows("tmix." + s, T, n, torch.float32) for s in ("rn", "kn", "vn"))
-        ops.time_mix_prep(proj[0], proj[1], proj[2], self.w0, rn, kn, vn, decay)
+        pair = ctx.ws.rows("tmix.pair", T, 2 * D, self.dtype)
+        ops.token_shift_concat(h, state, self.state_floats, ctx, pair)
+        proj = ctx.ws.rows("tmix.proj", T, self.width, self.dtype)
+        self.gemm_in(pair, proj)
+        rn, kn, vn, decay = (ctx.ws.rows("tmix." + s, T, n, torch.float32) for s in ("rn", "kn", "vn", "decay"))
+        ops.time_mix_prep(proj, self.offs["r"], self.offs["k"], self.offs["v"], self.inner_off, self.w2t, self.w0, rn, kn, vn, decay)
         o = ctx.ws.rows("tmix.o", T, n, torch.float32)
         ops.delta_rule_bonus(rn, kn, vn, decay, self.bonus, state, ctx, self.heads, self.dim, o)
         gated = ctx.ws.rows("tmix.gated", T, n, self.dtype)
-        ops.time_mix_out(o, proj[3], self.norm_w, self.eps, gated, self.heads, self.dim, h, state, self.state_floats, ctx)
+        ops.time_mix_out(o, proj[:, self.offs["g"]:self.offs["g"] + n], self.norm_w, self.eps, gated, self.heads, self.dim, h, state, self.state_floats, ctx)
         out = ctx.ws.rows("tmix.mixed", T, D, self.dtype)
         if self._capacity is None:
             self._capacity = ops.partial_capacity(ctx.ws.max_rows, self.gemm_o.N, self.gemm_o.K)
