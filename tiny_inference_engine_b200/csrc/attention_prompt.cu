@@ -156,6 +156,7 @@ __global__ void __launch_bounds__(kPromptThreads) attn_prompt_tma_kernel(const _
       if (a.r1 != nullptr && row < rows) row_r1[half] = a.r1[kvh * G + row % G], row_r2[half] = a.r2[kvh * G + row % G];
     }
     const float scale = a.scale_log2 * 0.6931471805599453f;
+    const float inv_cap = a.softcap > 0.0f ? 1.0f / a.softcap : 0.0f;
     const bool warp_has_rows = row0 + warp * 16 < rows;
     const int warp_hi = warp_has_rows ? pos0 + min(rows - 1, row0 + warp * 16 + 15) / G : -1;   // largest position of the warp's rows
     const int warp_lo = warp_has_rows ? pos0 + (row0 + warp * 16) / G : -1;                     // smallest
@@ -195,8 +196,10 @@ __global__ void __launch_bounds__(kPromptThreads) attn_prompt_tma_kernel(const _
               float v = sc[j][e] * a.scale_log2;
               if (shaped && ok) {
                 v = sc[j][e] * scale;
-                if (a.softcap > 0.0f) v = a.softcap * tanhf(v / a.softcap);
-                if (a.r1 != nullptr) v -= row_r1[e >> 1] * log1pf(row_r2[e >> 1] * static_cast<float>(pos - key));
+                // float arithmetic on the fast exponential and logarithm (absolute error about 1e-6 of a score, far below what the
+                // bfloat16 products of this kernel carry): tanh(z) = 1 - 2 / (exp(2 z) + 1); ln(1 + x) with x >= 0
+                if (a.softcap > 0.0f) v = a.softcap * (1.0f - __fdividef(2.0f, __expf(2.0f * v * inv_cap) + 1.0f));
+                if (a.r1 != nullptr) v -= row_r1[e >> 1] * __logf(fmaf(row_r2[e >> 1], static_cast<float>(pos - key), 1.0f));
                 v *= 1.4426950408889634f;
               }
               sc[j][e] = ok ? v : -INFINITY;

@@ -252,6 +252,11 @@ __global__ void __launch_bounds__(128) attention_split_kernel(AttnArgs a, const 
 // (acc, max, sum) where attention_split_kernel leaves them, for the same merge.
 constexpr int kGroupTile = 32;
 
+// 16 bytes from global to shared memory without a stop in a register: all of a thread's copies of a tile are in flight together.
+__device__ __forceinline__ void group_copy16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))), "l"(src) : "memory");
+}
+
 template <typename T, int DPL>
 __global__ void __launch_bounds__(1024) attention_group_split_kernel(AttnArgs a, const int* __restrict__ seq_list, int n_list,
                                                                      int split_keys, int max_splits, float* __restrict__ scratch,
@@ -302,9 +307,8 @@ __global__ void __launch_bounds__(1024) attention_group_split_kernel(AttnArgs a,
       const int pieces = k_ld / V;
       for (int i = threadIdx.x; i < kGroupTile * pieces; i += blockDim.x) {
         const int kk = i / pieces, p = (i % pieces) * V;
-        uint4 val = make_uint4(0u, 0u, 0u, 0u);
-        if (rows[kk] >= 0) val = *reinterpret_cast<const uint4*>(kc + static_cast<long long>(rows[kk]) * k_ld + p);
-        *reinterpret_cast<uint4*>(k_tile + kk * k_row + p) = val;
+        if (rows[kk] >= 0) group_copy16(k_tile + kk * k_row + p, kc + static_cast<long long>(rows[kk]) * k_ld + p);
+        else *reinterpret_cast<uint4*>(k_tile + kk * k_row + p) = make_uint4(0u, 0u, 0u, 0u);
       }
     } else {
       for (int i = threadIdx.x; i < kGroupTile * k_ld; i += blockDim.x) {
@@ -316,9 +320,8 @@ __global__ void __launch_bounds__(1024) attention_group_split_kernel(AttnArgs a,
       const int pieces = v_ld / V;
       for (int i = threadIdx.x; i < kGroupTile * pieces; i += blockDim.x) {
         const int kk = i / pieces, p = (i % pieces) * V;
-        uint4 val = make_uint4(0u, 0u, 0u, 0u);
-        if (rows[kk] >= 0) val = *reinterpret_cast<const uint4*>(vc + static_cast<long long>(rows[kk]) * v_ld + p);
-        *reinterpret_cast<uint4*>(v_tile + kk * v_ld + p) = val;
+        if (rows[kk] >= 0) group_copy16(v_tile + kk * v_ld + p, vc + static_cast<long long>(rows[kk]) * v_ld + p);
+        else *reinterpret_cast<uint4*>(v_tile + kk * v_ld + p) = make_uint4(0u, 0u, 0u, 0u);
       }
     } else {
       for (int i = threadIdx.x; i < kGroupTile * v_ld; i += blockDim.x) {
@@ -326,6 +329,7 @@ __global__ void __launch_bounds__(1024) attention_group_split_kernel(AttnArgs a,
         v_tile[kk * v_ld + p] = rows[kk] >= 0 ? vc[static_cast<long long>(rows[kk]) * v_ld + p] : T(0.0f);
       }
     }
+    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");      // the copies of this thread; the barrier does the rest
     __syncthreads();
     const int j = base + lane;
     const bool valid = j <= hi;
@@ -354,13 +358,31 @@ __global__ void __launch_bounds__(1024) attention_group_split_kernel(AttnArgs a,
     m = m_new;
 #pragma unroll
     for (int e = 0; e < DPL; ++e) acc[e] *= corr;
+    if (DPL % 4 == 0 && v_ld % 4 == 0 && a.v_dim % DPL == 0) {      // a lane's value elements in pieces of four
+      const bool mine = d0 < a.v_dim;
 #pragma unroll 4
-    for (int jj = 0; jj < kGroupTile; ++jj) {
-      const float pj = __shfl_sync(0xffffffffu, p, jj);
-      const T* vr = v_tile + jj * v_ld + d0;
+      for (int jj = 0; jj < kGroupTile; ++jj) {
+        const float pj = __shfl_sync(0xffffffffu, p, jj);
+        if (mine) {
+          const T* vr = v_tile + jj * v_ld + d0;
 #pragma unroll
-      for (int e = 0; e < DPL; ++e)
-        if (d0 + e < a.v_dim) acc[e] = fmaf(pj, ld(vr + e), acc[e]);
+          for (int e4 = 0; e4 < DPL / 4; ++e4) {
+            float v4[4];
+            load4(vr + 4 * e4, v4);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[4 * e4 + e] = fmaf(pj, v4[e], acc[4 * e4 + e]);
+          }
+        }
+      }
+    } else {
+#pragma unroll 4
+      for (int jj = 0; jj < kGroupTile; ++jj) {
+        const float pj = __shfl_sync(0xffffffffu, p, jj);
+        const T* vr = v_tile + jj * v_ld + d0;
+#pragma unroll
+        for (int e = 0; e < DPL; ++e)
+          if (d0 + e < a.v_dim) acc[e] = fmaf(pj, ld(vr + e), acc[e]);
+      }
     }
   }
   float* dst = scratch + ((static_cast<long long>(li) * a.q_heads + h) * max_splits + split) * (a.v_dim + 2);

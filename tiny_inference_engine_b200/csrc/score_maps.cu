@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(128) slice_norm_append_kernel(T* __restrict__ 
   const int slot = write_kv ? slots[t] : -1;
   const long long page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
   const int slices = (wq ? nq : 0) + (slot >= 0 ? nk : 0);
-  for (int i = warp; i < slices; i += warps) {
+  for (int i = blockIdx.y * warps + warp; i < slices; i += gridDim.y * warps) {
     const bool is_q = wq != nullptr && i < nq;
     const int j = is_q ? i : i - (wq ? nq : 0);
     T* src = row + (is_q ? q_off : k_off) + j * dim;
@@ -57,7 +57,7 @@ __global__ void __launch_bounds__(128) slice_norm_append_kernel(T* __restrict__ 
     }
   }
   if (slot >= 0) {
-    for (int j = threadIdx.x; j < v_width; j += blockDim.x) {
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < v_width; j += gridDim.y * blockDim.x) {
       const int c = j / v_row, d = j % v_row;
       v_cache[((page * kv_heads + c) * page_size + off) * v_row + d] = row[v_off + j];
     }
@@ -122,12 +122,14 @@ TIE_API int tie_slice_norm_append(int dtype, void* proj, long long stride, int q
                 "slice_norm_append: %d key slices of %d and %d value columns do not fill %d cached heads of %d and %d", nk, dim,
                 v_width, kv_heads, k_row, v_row);
   if (tokens == 0 || (!write_kv && wq == nullptr)) return kOk;
+  const int slice_tiles = tokens >= 512 ? 1 : min(ceil_div((wq ? nq : 0) + (write_kv ? nk : 0), 4), 32);      // few rows: several blocks a row
+  const dim3 grid(tokens, slice_tiles > 0 ? slice_tiles : 1);
   if (dtype == TIE_F32) {
-    TIE_LAUNCH((slice_norm_append_kernel<float>), tokens, 128, 0, s, static_cast<float*>(proj), stride, q_off, nq, k_off, nk, v_off,
+    TIE_LAUNCH((slice_norm_append_kernel<float>), grid, 128, 0, s, static_cast<float*>(proj), stride, q_off, nq, k_off, nk, v_off,
                v_width, dim, wq, wk, eps, slots, static_cast<float*>(k_cache), static_cast<float*>(v_cache), kv_heads, k_row, v_row,
                page_size, write_kv);
   } else if (dtype == TIE_BF16) {
-    TIE_LAUNCH((slice_norm_append_kernel<__nv_bfloat16>), tokens, 128, 0, s, static_cast<__nv_bfloat16*>(proj), stride, q_off, nq,
+    TIE_LAUNCH((slice_norm_append_kernel<__nv_bfloat16>), grid, 128, 0, s, static_cast<__nv_bfloat16*>(proj), stride, q_off, nq,
                k_off, nk, v_off, v_width, dim, wq, wk, eps, slots, static_cast<__nv_bfloat16*>(k_cache),
                static_cast<__nv_bfloat16*>(v_cache), kv_heads, k_row, v_row, page_size, write_kv);
   } else {

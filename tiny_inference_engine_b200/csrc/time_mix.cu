@@ -27,14 +27,15 @@ __global__ void __launch_bounds__(256) token_shift_concat_kernel(const T* __rest
   const int slot = state_slots[s];
   const float* kept = (first && positions[t] > 0 && slot >= 0) ? state + slot * state_stride + prev_off : nullptr;
   T* row = out + t * 2 * D;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+  for (int d = blockIdx.y * blockDim.x + threadIdx.x; d < D; d += gridDim.y * blockDim.x) {
     row[d] = h[t * D + d];
     if (first) st(row + D + d, kept ? kept[d] : 0.0f);
     else row[D + d] = h[(t - 1) * D + d];
   }
 }
 
-// One block a token: tanh of the inner channels once into shared memory, then a thread a decay channel.
+// Blocks of 256 decay channels of a token (a few tokens fill the GPU that way): tanh of the inner channels into shared memory,
+// then a thread a decay channel.
 template <typename T>
 __global__ void __launch_bounds__(256) time_mix_prep_kernel(const T* __restrict__ proj, long long stride, int r_off, int k_off, int v_off,
                                                             int inner_off, int rank, const float* __restrict__ w2t,
@@ -46,7 +47,7 @@ __global__ void __launch_bounds__(256) time_mix_prep_kernel(const T* __restrict_
   const T* row = proj + t * stride;
   for (int j = threadIdx.x; j < rank; j += blockDim.x) inner[j] = tanhf(ld(row + inner_off + j));
   __syncthreads();
-  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < n; c += gridDim.y * blockDim.x) {
     rn[t * n + c] = ld(row + r_off + c);
     kn[t * n + c] = ld(row + k_off + c);
     vn[t * n + c] = ld(row + v_off + c);
@@ -108,10 +109,11 @@ TIE_API int tie_token_shift_concat(int dtype, const void* h, const float* state,
                                    void* out, int tokens, int D, cudaStream_t s) {
   TIE_REQUIRE(tokens >= 0 && D > 0, "token_shift_concat: bad sizes");
   if (tokens == 0) return kOk;
+  const int col_tiles = tokens >= 512 ? 1 : min(ceil_div(D, 256), 64);      // few rows: several blocks a row
   TIE_BY_DTYPE(dtype,
-               TIE_LAUNCH((token_shift_concat_kernel<float>), tokens, 256, 0, s, static_cast<const float*>(h), state, state_stride, prev_off,
+               TIE_LAUNCH((token_shift_concat_kernel<float>), dim3(tokens, col_tiles), 256, 0, s, static_cast<const float*>(h), state, state_stride, prev_off,
                           seq_of_row, query_start, positions, state_slots, static_cast<float*>(out), D),
-               TIE_LAUNCH((token_shift_concat_kernel<__nv_bfloat16>), tokens, 256, 0, s, static_cast<const __nv_bfloat16*>(h), state,
+               TIE_LAUNCH((token_shift_concat_kernel<__nv_bfloat16>), dim3(tokens, col_tiles), 256, 0, s, static_cast<const __nv_bfloat16*>(h), state,
                           state_stride, prev_off, seq_of_row, query_start, positions, state_slots, static_cast<__nv_bfloat16*>(out), D));
   TIE_RETURN_LAUNCH("token_shift_concat");
 }
@@ -122,10 +124,11 @@ TIE_API int tie_time_mix_prep(int dtype, const void* proj, long long stride, int
   TIE_REQUIRE(tokens >= 0 && n > 0 && rank > 0 && rank <= 8192, "time_mix_prep: bad sizes tokens=%d n=%d inner=%d", tokens, n, rank);
   if (tokens == 0) return kOk;
   const size_t smem = static_cast<size_t>(rank) * sizeof(float);
+  const int col_tiles = tokens >= 512 ? 1 : min(ceil_div(n, 256), 64);
   TIE_BY_DTYPE(dtype,
-               TIE_LAUNCH((time_mix_prep_kernel<float>), tokens, 256, smem, s, static_cast<const float*>(proj), stride, r_off, k_off, v_off,
+               TIE_LAUNCH((time_mix_prep_kernel<float>), dim3(tokens, col_tiles), 256, smem, s, static_cast<const float*>(proj), stride, r_off, k_off, v_off,
                           inner_off, rank, w2t, w0, rn, kn, vn, decay, n),
-               TIE_LAUNCH((time_mix_prep_kernel<__nv_bfloat16>), tokens, 256, smem, s, static_cast<const __nv_bfloat16*>(proj), stride, r_off,
+               TIE_LAUNCH((time_mix_prep_kernel<__nv_bfloat16>), dim3(tokens, col_tiles), 256, smem, s, static_cast<const __nv_bfloat16*>(proj), stride, r_off,
                           k_off, v_off, inner_off, rank, w2t, w0, rn, kn, vn, decay, n));
   TIE_RETURN_LAUNCH("time_mix_prep");
 }
