@@ -41,6 +41,7 @@ struct PromptArgs {
   float softcap;          // > 0: score <- softcap * tanh(score / softcap), ahead of the bias
   const float* r1;        // [q_heads] or null: score -= r1[h] * ln(1 + r2[h] * (position - key position))
   const float* r2;
+  int out_f32;            // != 0: `out` holds float rows (what follows combines heads' outputs and wants them unrounded)
 };
 
 // The first key that position `pos` sees.
@@ -218,10 +219,18 @@ __global__ void __launch_bounds__(kPromptThreads) attn_prompt_tma_kernel(const _
       const int row = row0 + warp * 16 + g + 8 * half;
       if (row >= rows) continue;
       const float inv = l[half] > 0.0f ? 1.0f / l[half] : 0.0f;
-      __nv_bfloat16* o = a.out + ((static_cast<long long>(t0 + row / G) * a.q_heads + kvh * G + row % G) * v_slices + v_slice) * DH;
+      const long long at = ((static_cast<long long>(t0 + row / G) * a.q_heads + kvh * G + row % G) * v_slices + v_slice) * DH;
+      if (a.out_f32) {
+        float* o = reinterpret_cast<float*>(a.out) + at;
 #pragma unroll
-      for (int j = 0; j < DH / 8; ++j) {
-        *reinterpret_cast<uint32_t*>(o + j * 8 + tq * 2) = pack_bf16(acc[j][2 * half] * inv, acc[j][2 * half + 1] * inv);
+        for (int j = 0; j < DH / 8; ++j)
+          *reinterpret_cast<float2*>(o + j * 8 + tq * 2) = make_float2(acc[j][2 * half] * inv, acc[j][2 * half + 1] * inv);
+      } else {
+        __nv_bfloat16* o = a.out + at;
+#pragma unroll
+        for (int j = 0; j < DH / 8; ++j) {
+          *reinterpret_cast<uint32_t*>(o + j * 8 + tq * 2) = pack_bf16(acc[j][2 * half] * inv, acc[j][2 * half + 1] * inv);
+        }
       }
     }
   }
@@ -262,7 +271,7 @@ static int prompt_tma(const void* q, long long q_stride, const void* k_cache, co
                       const int* query_start, const int* context_lens, const int* block_tables, int max_blocks, int n_seqs,
                       int max_queries, int q_heads, int kv_heads, int head_dim, int page_size, int pages, int window,
                       float scale, int exact_weights, cudaStream_t s, int cache_heads = 0, int k_ld = 0, int v_ld = 0, int v_shift = 0,
-                      int chunk = 0, float softcap = 0.0f, const float* r1 = nullptr, const float* r2 = nullptr) {
+                      int chunk = 0, float softcap = 0.0f, const float* r1 = nullptr, const float* r2 = nullptr, int out_f32 = 0) {
   TIE_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256, "attention_prompt: head_dim %d is not 64, 128 or 256", head_dim);
   TIE_REQUIRE(q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0 && q_heads / kv_heads <= 16,
               "attention_prompt: %d query heads over %d kv heads (at most 16 per group)", q_heads, kv_heads);
@@ -287,7 +296,7 @@ static int prompt_tma(const void* q, long long q_stride, const void* k_cache, co
   TIE_REQUIRE(status_word() != nullptr, "attention_prompt: cannot allocate the status word");
   PromptArgs a{static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out), query_start, context_lens, block_tables,
                status_word(), q_stride, max_blocks, q_heads, kv_heads, page_size, shift, window, scale * 1.4426950408889634f,
-               exact_weights, cache_heads, k_ld, v_ld, v_shift, chunk, softcap, r1, r2};
+               exact_weights, cache_heads, k_ld, v_ld, v_shift, chunk, softcap, r1, r2, out_f32};
   const int max_rows = max_queries * (q_heads / kv_heads);
   int st = kOk;
   if (head_dim == 64) st = launch_prompt_tma<64>(km, vm, a, n_seqs, max_rows, s);
@@ -317,7 +326,7 @@ TIE_API int tie_attention_prompt_tma_exact(const void* q, long long q_stride, co
 // Score maps over slices of wider cached rows (the fields of PromptArgs behind exact_weights), with the softmax weights kept
 // to 16 bits of mantissa: kv head v of the launch reads cached head v % cache_heads, its DH key elements at column
 // (v / cache_heads) * DH of key rows of k_ld and its DH value elements at column ((v / cache_heads + v_shift) % (v_ld / DH)) * DH
-// of value rows of v_ld; out is [T, q_heads, v_ld / DH, DH] and the launch fills the slice of its value column. Chunks, a cap on
+// of value rows of v_ld; out is float [T, q_heads, v_ld / DH, DH] and the launch fills the slice of its value column. Chunks, a cap on
 // the scores and a bias by the logarithm of the distance are options.
 TIE_API int tie_attention_prompt_maps(const void* q, long long q_stride, const void* k_cache, const void* v_cache, void* out,
                                       const int* query_start, const int* context_lens, const int* block_tables, int max_blocks,
@@ -326,5 +335,5 @@ TIE_API int tie_attention_prompt_maps(const void* q, long long q_stride, const v
                                       float softcap, const float* r1, const float* r2, cudaStream_t s) {
   return prompt_tma(q, q_stride, k_cache, v_cache, out, query_start, context_lens, block_tables, max_blocks, n_seqs, max_queries,
                     q_heads, kv_heads, head_dim, page_size, pages, window, scale, 1, s, cache_heads, k_ld, v_ld, v_shift, chunk, softcap,
-                    r1, r2);
+                    r1, r2, 1);
 }

@@ -1458,12 +1458,12 @@ def attention_prompt_maps(q, k_cache, v_cache, out, query_start, context_lens, b
     """Prompt portions on the tensor cores (TMA-fed `mma.sync`, float scores and softmax, weights as two bfloat16 terms) for score
     maps over slices of wider cached rows: kv head v of `kv_heads` reads cached head v % cached heads, its `dim` key elements from column
     (v // cached heads) * dim and its `dim` value elements from column ((v // cached heads + v_shift) % slices) * dim, slices = value row / dim;
-    query heads v * (q_heads / kv_heads) .. read kv head v. out bfloat16 [T, q_heads, slices, dim]: the call fills the slice of its value
+    query heads v * (q_heads / kv_heads) .. read kv head v. out float32 [T, q_heads, slices, dim]: the call fills the slice of its value
     column. At most 16 query heads a kv head."""
     _dev(q, k_cache, v_cache, out, query_start, context_lens, block_tables, r1, r2)
     slices = v_cache.shape[3] // dim
-    _need(out.dtype == torch.bfloat16 and out.is_contiguous() and out.shape == (q.shape[0], q_heads * slices * dim),
-          "attention_prompt_maps: out must be bfloat16 [T, q_heads * slices * dim]")
+    _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape == (q.shape[0], q_heads * slices * dim),
+          "attention_prompt_maps: out must be float32 [T, q_heads * slices * dim]")
     _need(q_heads % kv_heads == 0 and q_heads // kv_heads <= 16 and kv_heads % k_cache.shape[1] == 0, "attention_prompt_maps: impossible head counts")
     call("tie_attention_prompt_maps", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), query_start.data_ptr(),
          context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], n_seqs, max_queries, q_heads, kv_heads, dim, k_cache.shape[2],

@@ -77,19 +77,16 @@ class _SliceAttention(Mixer):
         self._capacity = None
 
     def _attend(self, q, cache, ctx, g, width, q_heads, group, sub_div, sub_count, tensor_cores=None, chunk=0, softcap=0.0, r1=None, r2=None):
-        """The step's rows through attention: [(first row, end row, buffer [T, width])]. Rows of sequences that bring several tokens
-        come first; they go through `tensor_cores(out)` (bfloat16 out) where the caller gives it, else through the CUDA-core kernel
-        (float32 out). Sequences that bring one token go through the split kernel (float32 out)."""
-        T, m, spans = q.shape[0], ctx.multi_rows, []
+        """The step's rows through attention into one float32 buffer [T, width]. Rows of sequences that bring several tokens come first;
+        they go through `tensor_cores(out)` where the caller gives it, else through the CUDA-core kernel. Sequences that bring one
+        token go through the split kernel."""
+        T, m = q.shape[0], ctx.multi_rows
+        out = ctx.ws.rows(self.tag + ".attended", T, width, torch.float32)
         if m > 0 and tensor_cores is not None:
-            out16 = ctx.ws.rows(self.tag + ".attended16", T, width, self.dtype)
-            tensor_cores(out16)
-            spans.append((0, m, out16))
-        out = ctx.ws.rows(self.tag + ".attended", T, width, torch.float32) if ctx.single_count > 0 or len(spans) == 0 else None
-        if m > 0 and tensor_cores is None:
+            tensor_cores(out)
+        elif m > 0:
             ops.attention_maps_rows(q, cache.k, cache.v, out, ctx.seq_of_row, ctx.query_start, ctx.context_lens, g.block_tables,
                                     m, q_heads, self.dim, group, sub_div, sub_count, self.scale, chunk=chunk, softcap=softcap, r1=r1, r2=r2)
-            spans.append((0, m, out))
         if ctx.single_count > 0:
             longest = ctx.single_max_context if chunk <= 0 else min(ctx.single_max_context, chunk)
             # splits enough to fill the SMs with warps of (sequence, head, split), none shorter than 32 keys; the split size follows from
@@ -104,8 +101,7 @@ class _SliceAttention(Mixer):
             ops.attention_maps_split(q, cache.k, cache.v, out, ctx.query_start, ctx.context_lens, g.block_tables, q_heads, self.dim,
                                      group, sub_div, sub_count, self.scale, ctx.single_seqs, ctx.single_count, split_keys, max_splits, scratch,
                                      chunk=chunk, softcap=softcap, r1=r1, r2=r2)
-            spans.append((m, T, out))
-        return spans
+        return out
 
     def _project_out(self, heads_out, ctx):
         T = heads_out.shape[0]
@@ -183,9 +179,9 @@ class DifferentialAttention(_SliceAttention):
                                                                  ctx.multi_seqs, ctx.multi_max_queries, 2 * H, 2 * self.kv_heads, self.dim,
                                                                  self.scale, chunk=self.chunk)
         heads_out = ctx.ws.rows(self.tag + ".heads", T, self.o_dim, self.dtype)
-        for lo, hi, maps in self._attend(q, cache, ctx, g, 2 * H * self.vdim, 2 * H, per, H, 2, tensor_cores, chunk=self.chunk):
-            gate = proj[lo:hi, self.g_off:self.g_off + self.o_dim] if self.output_gate else None
-            ops.diff_combine(maps[lo:hi], gate, self.lam, 1.0 - self.diff, self.eps, heads_out[lo:hi], H, self.vdim)
+        maps = self._attend(q, cache, ctx, g, 2 * H * self.vdim, 2 * H, per, H, 2, tensor_cores, chunk=self.chunk)
+        gate = proj[:, self.g_off:self.g_off + self.o_dim] if self.output_gate else None
+        ops.diff_combine(maps, gate, self.lam, 1.0 - self.diff, self.eps, heads_out, H, self.vdim)
         return self._project_out(heads_out, ctx)
 
 
@@ -244,9 +240,9 @@ class TalkingHeadsAttention(_SliceAttention):
                                               ctx.multi_max_queries, H, G, self.dim, self.scale, v_shift=shift, softcap=self.softcap,
                                               r1=self.r1, r2=self.r2)
         heads_out = ctx.ws.rows(self.tag + ".heads", T, self.o_dim, self.dtype)
-        for lo, hi, pairs in self._attend(q, cache, ctx, g, H * self.v_dim, H, H // G, H // G, G, tensor_cores, softcap=self.softcap,
-                                          r1=self.r1, r2=self.r2):       # pairs [T, H, G, vdim]
-            ops.head_talk(pairs[lo:hi], self.mix, heads_out[lo:hi], H, G, self.vdim)
+        pairs = self._attend(q, cache, ctx, g, H * self.v_dim, H, H // G, H // G, G, tensor_cores, softcap=self.softcap, r1=self.r1,
+                             r2=self.r2)       # [T, H, G, vdim]
+        ops.head_talk(pairs, self.mix, heads_out, H, G, self.vdim)
         return self._project_out(heads_out, ctx)
 
 
