@@ -154,13 +154,30 @@ __global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ out
 
 // One hidden layer's activation in two branches that meet at zero with the slope 1/2:
 //   z > 0: c_pos z^2 + z / 2;   z <= 0: c_neg (exp(z) - 1 - z) + z / 2.
+__device__ __forceinline__ float two_branch(float v, float c_pos, float c_neg) {
+  return v > 0.0f ? fmaf(c_pos * v, v, 0.5f * v) : fmaf(c_neg, expm1f(v) - v, 0.5f * v);
+}
+
 template <typename T>
 __global__ void two_branch_unit_kernel(const T* __restrict__ z, T* __restrict__ out, long long total, float c_pos, float c_neg) {
   pdl_sync();
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= total) return;
-  const float v = ld(z + i);
-  st(out + i, v > 0.0f ? fmaf(c_pos * v, v, 0.5f * v) : fmaf(c_neg, expm1f(v) - v, 0.5f * v));
+  st(out + i, two_branch(ld(z + i), c_pos, c_neg));
+}
+
+// 16 bytes a thread.
+template <typename T>
+__global__ void two_branch_unit_vec_kernel(const T* __restrict__ z, T* __restrict__ out, long long pieces, float c_pos, float c_neg) {
+  pdl_sync();
+  constexpr int V = Vec16<T>::N;
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= pieces) return;
+  Vec16<T> v;
+  v.load(z + i * V);
+#pragma unroll
+  for (int e = 0; e < V; ++e) v.v[e] = two_branch(v.v[e], c_pos, c_neg);
+  v.store(out + i * V);
 }
 
 template <typename T>
@@ -299,12 +316,21 @@ TIE_API int tie_glu_clamped(int dtype, const void* gu, void* out, int tokens, in
 TIE_API int tie_two_branch_unit(int dtype, const void* z, void* out, long long total, float c_pos, float c_neg, cudaStream_t s) {
   TIE_REQUIRE(total >= 0, "two_branch_unit: bad size");
   if (total == 0) return kOk;
+  const bool aligned = reinterpret_cast<uintptr_t>(z) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
   if (dtype == TIE_F32) {
-    TIE_LAUNCH((two_branch_unit_kernel<float>), ceil_div(total, 256), 256, 0, s, static_cast<const float*>(z), static_cast<float*>(out), total,
-               c_pos, c_neg);
+    if (aligned && total % 4 == 0)
+      TIE_LAUNCH((two_branch_unit_vec_kernel<float>), ceil_div(total / 4, 256), 256, 0, s, static_cast<const float*>(z), static_cast<float*>(out),
+                 total / 4, c_pos, c_neg);
+    else
+      TIE_LAUNCH((two_branch_unit_kernel<float>), ceil_div(total, 256), 256, 0, s, static_cast<const float*>(z), static_cast<float*>(out), total,
+                 c_pos, c_neg);
   } else if (dtype == TIE_BF16) {
-    TIE_LAUNCH((two_branch_unit_kernel<__nv_bfloat16>), ceil_div(total, 256), 256, 0, s, static_cast<const __nv_bfloat16*>(z),
-               static_cast<__nv_bfloat16*>(out), total, c_pos, c_neg);
+    if (aligned && total % 8 == 0)
+      TIE_LAUNCH((two_branch_unit_vec_kernel<__nv_bfloat16>), ceil_div(total / 8, 256), 256, 0, s, static_cast<const __nv_bfloat16*>(z),
+                 static_cast<__nv_bfloat16*>(out), total / 8, c_pos, c_neg);
+    else
+      TIE_LAUNCH((two_branch_unit_kernel<__nv_bfloat16>), ceil_div(total, 256), 256, 0, s, static_cast<const __nv_bfloat16*>(z),
+                 static_cast<__nv_bfloat16*>(out), total, c_pos, c_neg);
   } else {
     set_error("unknown dtype code %d", dtype);
     return kBadArgument;

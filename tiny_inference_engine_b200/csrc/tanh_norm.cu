@@ -50,6 +50,53 @@ __global__ void __launch_bounds__(256) add_tanh_norm_kernel(float* __restrict__ 
   }
 }
 
+// Four columns a thread (D a multiple of four, every pointer on a 16-byte boundary; the terms' rows likewise).
+template <typename T>
+__device__ __forceinline__ void term_add4(const Term& term, long long at, float (&v)[4]) {
+  if (term.tensor != nullptr) {
+    float d[4];
+    load4(static_cast<const T*>(term.tensor) + at, d);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) v[e] = fmaf(term.scale, d[e], v[e]);
+  } else if (term.partial != nullptr) {
+    float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int z = 0; z < term.splits; ++z) {
+      float d[4];
+      load4(term.partial + z * term.stride + at, d);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sum[e] += d[e];
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) v[e] = fmaf(term.scale, sum[e], v[e]);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) add_tanh_norm_vec4_kernel(float* __restrict__ x, Term a, Term b, const int* __restrict__ rows,
+                                                                 float alpha, const float* __restrict__ w, const float* __restrict__ bias,
+                                                                 T* __restrict__ out, int n, int D) {
+  pdl_sync();
+  const int quads = D / 4;
+  const long long total = static_cast<long long>(n) * quads;
+  const bool adds = a.tensor || a.partial || b.tensor || b.partial;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int d = static_cast<int>(i % quads) * 4;
+    const long long r = rows ? rows[i / quads] : i / quads;
+    const long long at = r * D + d;
+    float v[4], ww[4], bb[4], o[4];
+    load4(x + at, v);
+    term_add4<T>(a, at, v);
+    term_add4<T>(b, at, v);
+    if (rows == nullptr && adds) store4(x + at, v);
+    load4(w + d, ww);
+    load4(bias + d, bb);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[e] = fmaf(tanhf(alpha * v[e]), ww[e], bb[e]);
+    store4(out + (i / quads) * D + d, o);
+  }
+}
+
 __global__ void __launch_bounds__(256) sinusoid_add_kernel(float* __restrict__ x, const int* __restrict__ positions, int T,
                                                            int D, double log_base) {
   pdl_sync();
@@ -79,11 +126,20 @@ TIE_API int tie_add_tanh_norm(int dtype, float* x, const void* a, const float* a
   if (n == 0) return kOk;
   const Term ta{a, a_part, a_stride, a_splits, a_scale}, tb{b, b_part, b_stride, b_splits, b_scale};
   const int blocks = static_cast<int>(min(static_cast<long long>(148 * 8), (static_cast<long long>(n) * D + 255) / 256));
+  auto on16 = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  const bool vec4 = D % 4 == 0 && on16(x) && on16(a) && on16(a_part) && on16(b) && on16(b_part) && on16(w) && on16(bias) && on16(out) &&
+                    a_stride % 4 == 0 && b_stride % 4 == 0;
+  const int blocks4 = static_cast<int>(min(static_cast<long long>(148 * 8), (static_cast<long long>(n) * (D / 4) + 255) / 256));
   if (dtype == TIE_F32) {
-    TIE_LAUNCH((add_tanh_norm_kernel<float>), blocks, 256, 0, s, x, ta, tb, rows, alpha, w, bias, static_cast<float*>(out), n, D);
+    if (vec4) TIE_LAUNCH((add_tanh_norm_vec4_kernel<float>), blocks4, 256, 0, s, x, ta, tb, rows, alpha, w, bias, static_cast<float*>(out), n, D);
+    else TIE_LAUNCH((add_tanh_norm_kernel<float>), blocks, 256, 0, s, x, ta, tb, rows, alpha, w, bias, static_cast<float*>(out), n, D);
   } else if (dtype == TIE_BF16) {
-    TIE_LAUNCH((add_tanh_norm_kernel<__nv_bfloat16>), blocks, 256, 0, s, x, ta, tb, rows, alpha, w, bias,
-               static_cast<__nv_bfloat16*>(out), n, D);
+    if (vec4)
+      TIE_LAUNCH((add_tanh_norm_vec4_kernel<__nv_bfloat16>), blocks4, 256, 0, s, x, ta, tb, rows, alpha, w, bias,
+                 static_cast<__nv_bfloat16*>(out), n, D);
+    else
+      TIE_LAUNCH((add_tanh_norm_kernel<__nv_bfloat16>), blocks, 256, 0, s, x, ta, tb, rows, alpha, w, bias,
+                 static_cast<__nv_bfloat16*>(out), n, D);
   } else {
     set_error("unknown dtype code %d", dtype);
     return kBadArgument;
