@@ -358,7 +358,23 @@ __global__ void __launch_bounds__(1024) attention_group_split_kernel(AttnArgs a,
     m = m_new;
 #pragma unroll
     for (int e = 0; e < DPL; ++e) acc[e] *= corr;
-    if (DPL % 4 == 0 && v_ld % 4 == 0 && a.v_dim % DPL == 0) {      // a lane's value elements in pieces of four
+    if (DPL % V == 0 && v_vec && a.v_dim % DPL == 0) {      // a lane's value elements in 16-byte pieces: no two lanes on a bank
+      const bool mine = d0 < a.v_dim;
+#pragma unroll 4
+      for (int jj = 0; jj < kGroupTile; ++jj) {
+        const float pj = __shfl_sync(0xffffffffu, p, jj);
+        if (mine) {
+          const T* vr = v_tile + jj * v_ld + d0;
+#pragma unroll
+          for (int ev = 0; ev < DPL / V; ++ev) {
+            Vec16<T> vv;
+            vv.load(vr + V * ev);
+#pragma unroll
+            for (int e = 0; e < V; ++e) acc[V * ev + e] = fmaf(pj, vv.v[e], acc[V * ev + e]);
+          }
+        }
+      }
+    } else if (DPL % 4 == 0 && v_ld % 4 == 0 && a.v_dim % DPL == 0) {      // in pieces of four
       const bool mine = d0 < a.v_dim;
 #pragma unroll 4
       for (int jj = 0; jj < kGroupTile; ++jj) {

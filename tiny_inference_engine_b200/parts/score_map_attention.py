@@ -89,9 +89,9 @@ class _SliceAttention(Mixer):
                                     m, q_heads, self.dim, group, sub_div, sub_count, self.scale, chunk=chunk, softcap=softcap, r1=r1, r2=r2)
         if ctx.single_count > 0:
             longest = ctx.single_max_context if chunk <= 0 else min(ctx.single_max_context, chunk)
-            # splits enough to fill the SMs with warps of (sequence, head, split), none shorter than 32 keys; the split size follows from
+            # splits enough to fill the SMs four times over with blocks, none shorter than 32 keys; the split size follows from
             # the step's longest context and its count of single rows, so a row's sums depend on the batch by their order only
-            want = max(1, (16 * NUM_SMS) // max(1, ctx.single_count * q_heads))
+            want = max(1, (4 * NUM_SMS) // max(1, ctx.single_count * cache.k.shape[1]))       # a block per (sequence, cached head, split)
             split_keys = max(32, -(-math.ceil(longest / want) // 32) * 32)
             while math.ceil(longest / split_keys) > MAX_SPLITS:
                 split_keys *= 2
