@@ -136,6 +136,7 @@ SINGLE = {
     "talking_heads": plain.make_config([P(right_scale=0.0, mlp=None)], vocab=60, width=48),
     "talking_heads_one_kv_head_no_cap": plain.make_config([P(heads=5, kv_heads=1, dim=24, vdim=12, softcap=None, right_scale=0.0, mlp=None)], vocab=60, width=40),
     "talking_heads_a_kv_head_each": plain.make_config([P(heads=3, kv_heads=3, dim=10, vdim=34, softcap=2.0, right_scale=0.0, mlp=None)], vocab=60, width=40),
+    "talking_heads_value_rows_of_1200": plain.make_config([P(heads=6, kv_heads=3, dim=8, vdim=400, right_scale=0.0, mlp=None)], vocab=60, width=40),
     "recurrence": plain.make_config([P(left_scale=0.0, mlp=None)], vocab=60, width=48),
     "recurrence_large_heads": plain.make_config([P(left_scale=0.0, rheads=1, rdim=80, mlp=None), P(left_scale=0.0, rheads=5, rdim=6, mlp=None)], vocab=60, width=40),
     "both_halves": plain.make_config([P(mlp=None)], vocab=60, width=48),

@@ -420,7 +420,7 @@ static size_t group_split_smem(const AttnArgs& a, int* warps, int* k_pad) {
   const int k_ld = a.k_ld ? a.k_ld : a.head_dim, v_ld = a.v_ld ? a.v_ld : a.v_dim;
   *warps = per;
   *k_pad = 16 / static_cast<int>(sizeof(T));        // rows a 16-byte piece apart in the banks: lanes read a column of 16-byte pieces
-  if (per > 32 || a.v_ld != 0) return 0;
+  if (per > 32 || a.v_ld != 0 || a.v_dim > 1024) return 0;      // (64 registers a thread: no room for more than 32 sums a lane)
   const size_t bytes = static_cast<size_t>(per) * a.head_dim * 4 + kGroupTile * 4 + 16 +
                        static_cast<size_t>(kGroupTile) * (k_ld + *k_pad + v_ld) * sizeof(T);
   return bytes <= 96 * 1024 ? bytes : 0;
@@ -517,7 +517,8 @@ int launch_attention(const AttnArgs& a, const int* row_seq_unused, const int* se
   else if (dpl <= 4) TIE_ATTN_CASE(4);
   else if (dpl <= 8) TIE_ATTN_CASE(8);
   else if (dpl <= 16) TIE_ATTN_CASE(16);
-  else TIE_ATTN_CASE(32);
+  else if (dpl <= 32) TIE_ATTN_CASE(32);
+  else TIE_ATTN_CASE(64);
 #undef TIE_ATTN_CASE
   TIE_RETURN_LAUNCH("paged_attention_simt");
 }
@@ -538,7 +539,7 @@ static int check_attn(const AttnArgs& a, bool any_size = false) {
     TIE_REQUIRE(a.head_dim <= 256 || a.head_dim % 16 == 0, "attention: head_dim %d above 256 must be a multiple of 16",
                 a.head_dim);
   }
-  TIE_REQUIRE(a.v_dim > 0 && a.v_dim <= (any_size ? 1024 : 512), "attention: value heads of %d (1 to %d)", a.v_dim, any_size ? 1024 : 512);
+  TIE_REQUIRE(a.v_dim > 0 && a.v_dim <= (any_size ? 2048 : 512), "attention: value heads of %d (1 to %d)", a.v_dim, any_size ? 2048 : 512);
   TIE_REQUIRE(a.page_size > 0 && a.max_blocks > 0, "attention: bad page geometry");
   TIE_REQUIRE(a.window >= 0, "attention: negative window");
   return kOk;
